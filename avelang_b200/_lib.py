@@ -1,0 +1,77 @@
+"""ctypes binding of libavefp4.so (the C ABI in include/ave_fp4.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+Error convention mirrors the reference backend, which turns driver errors into
+``RuntimeError("ave-lang Error [CUDA]: ...")`` (python/avelang/backends/nvidia/driver.py:68-81).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+from . import build as _build
+
+_lock = threading.Lock()
+_lib = None
+_inited: set[int] = set()
+
+# every symbol include/ave_fp4.h declares
+EXPORTS = (
+    "ave_fp4_init", "ave_fp4_last_error", "ave_fp4_sf_bytes", "ave_fp4_workspace_bytes", "ave_fp4_amax",
+    "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count",
+)
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (without touching any GPU)."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.LIB_PATH
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m avelang_b200.build` (needs nvcc). "
+                "This package has no CPU or library fallback.")
+        L = ctypes.CDLL(path)
+        i64, i32, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+        L.ave_fp4_init.restype = i32
+        L.ave_fp4_init.argtypes = [i32]
+        L.ave_fp4_last_error.restype = ctypes.c_char_p
+        L.ave_fp4_last_error.argtypes = []
+        L.ave_fp4_sf_bytes.restype = i64
+        L.ave_fp4_sf_bytes.argtypes = [i64, i64, i32, i32]
+        L.ave_fp4_workspace_bytes.restype = i64
+        L.ave_fp4_workspace_bytes.argtypes = [i64, i64, i64, i32, i32, i32]
+        L.ave_fp4_amax.restype = i32
+        L.ave_fp4_amax.argtypes = [vp, i64, i64, i64, vp, vp]
+        L.ave_fp4_quantize.restype = i32
+        L.ave_fp4_quantize.argtypes = [vp, i64, i64, i64, i32, vp, vp, vp, vp, i32, vp]
+        L.ave_fp4_sf_to_tiled.restype = i32
+        L.ave_fp4_sf_to_tiled.argtypes = [vp, i64, i64, vp, vp]
+        L.ave_fp4_gemm.restype = i32
+        L.ave_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, i64, vp]
+        L.ave_fp4_check.restype = i32
+        L.ave_fp4_check.argtypes = [vp]
+        L.ave_fp4_sm_count.restype = i32
+        L.ave_fp4_sm_count.argtypes = []
+        _lib = L
+        return L
+
+
+def check(rc: int) -> None:
+    """Raise for a non-zero return code of the C ABI."""
+    if rc != 0:
+        msg = load().ave_fp4_last_error().decode("utf-8", "replace")
+        if not msg.startswith("ave-lang Error"):
+            msg = "ave-lang Error [CUDA]: " + msg
+        raise RuntimeError(f"{msg} (code {rc})")
+
+
+def ensure_init(device_index: int) -> ctypes.CDLL:
+    L = load()
+    if device_index not in _inited:
+        check(L.ave_fp4_init(device_index))
+        _inited.add(device_index)
+    return L

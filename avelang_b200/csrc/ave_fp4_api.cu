@@ -1,0 +1,455 @@
+// Host side of libavefp4: argument checks, tensor-map encoding, kernel selection and
+// launch behind the C ABI declared in include/ave_fp4.h.
+//
+// Launch conventions follow the reference's NVIDIA backend
+// (python/avelang/backends/nvidia/driver.py:284-311): raw device pointers, the
+// caller's stream, no synchronisation, errors reported to the caller (there as a
+// Python RuntimeError, here as a return code plus ave_fp4_last_error()).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/ave_fp4.h"
+#include "gemm_fp4_skinny_sm100.cuh"
+#include "gemm_fp4_sm100.cuh"
+#include "quantize_fp4.cuh"
+
+namespace {
+
+using namespace avefp4;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+    snprintf(g_err, sizeof(g_err), "ave-lang Error [CUDA]: %s: %s", what, cudaGetErrorString(e));
+    return static_cast<int>(e);
+}
+
+#define AVE_CUDA(call)                                         \
+    do {                                                       \
+        cudaError_t e__ = (call);                              \
+        if (e__ != cudaSuccess) return fail_cuda(e__, #call);  \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    int* status = nullptr;
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+
+// ----------------------------------------------------------------------------------
+// Kernel table.  One entry per instantiation so that attributes are set once at init.
+template <int CG, int BN, int VEC, int ST, int ACC>
+cudaError_t prepare_gemm() {
+    using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
+    return cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg::kSmemBytes);
+}
+
+template <int MP, int VEC, int ST>
+cudaError_t prepare_skinny() {
+    using Cfg = SkinnyConfig<MP, VEC, ST>;
+    return cudaFuncSetAttribute(gemm_fp4_skinny_kernel<MP, VEC, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg::kSmemBytes);
+}
+
+// Stage counts per tile shape (shared-memory budget 227 KB per CTA).
+constexpr int kSt1N128 = 5, kSt1N256 = 3, kSt2N256 = 5, kSt2N128 = 6;
+constexpr int kStSkinny16 = 8, kStSkinny32 = 8, kStSkinny64 = 7;
+
+cudaError_t prepare_all() {
+    cudaError_t e;
+#define PREP(x) if ((e = (x)) != cudaSuccess) return e;
+    PREP((prepare_gemm<1, 128, 16, kSt1N128, 2>()));
+    PREP((prepare_gemm<1, 128, 32, kSt1N128, 2>()));
+    PREP((prepare_gemm<1, 256, 16, kSt1N256, 1>()));
+    PREP((prepare_gemm<1, 256, 32, kSt1N256, 1>()));
+    PREP((prepare_gemm<2, 256, 16, kSt2N256, 1>()));
+    PREP((prepare_gemm<2, 256, 32, kSt2N256, 1>()));
+    PREP((prepare_gemm<2, 128, 16, kSt2N128, 2>()));
+    PREP((prepare_gemm<2, 128, 32, kSt2N128, 2>()));
+    PREP((prepare_skinny<16, 16, kStSkinny16>()));
+    PREP((prepare_skinny<16, 32, kStSkinny16>()));
+    PREP((prepare_skinny<32, 16, kStSkinny32>()));
+    PREP((prepare_skinny<32, 32, kStSkinny32>()));
+    PREP((prepare_skinny<64, 16, kStSkinny64>()));
+    PREP((prepare_skinny<64, 32, kStSkinny64>()));
+#undef PREP
+    return cudaSuccess;
+}
+
+int current_state(DeviceState** out) {
+    int dev = -1;
+    AVE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices || !g_dev[dev].ready)
+        return fail(-AVE_FP4_ERR_NOT_INIT, "ave_fp4_init(%d) has not been called for the current device", dev);
+    *out = &g_dev[dev];
+    return 0;
+}
+
+// ----------------------------------------------------------------------------------
+// Tensor maps.
+int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
+              const char* what) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {outer_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(-AVE_FP4_ERR_ARG,
+                    "tensor map for %s rejected (CUresult %d): base %p dims (%llu,%llu) stride %llu box (%u,%u)", what,
+                    static_cast<int>(r), base, static_cast<unsigned long long>(inner),
+                    static_cast<unsigned long long>(outer), static_cast<unsigned long long>(outer_stride_bytes),
+                    box_inner, box_outer);
+    return 0;
+}
+
+// packed E2M1 operand (rows, k/2 bytes): box = 128 bytes x box_rows, 128-byte swizzle
+int encode_packed(CUtensorMap* tm, const void* p, int64_t rows, int64_t k, uint32_t box_rows, const char* what) {
+    return encode_2d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, p, static_cast<uint64_t>(k / 2), static_cast<uint64_t>(rows),
+                     static_cast<uint64_t>(k / 2), 128, box_rows, CU_TENSOR_MAP_SWIZZLE_128B, what);
+}
+
+// tiled scale factors: one 512-byte tile per row of a (tiles, 128 x u32) matrix
+int encode_sf(CUtensorMap* tm, const void* p, int64_t rows, int64_t k, int vec, uint32_t box_tiles, const char* what) {
+    const int64_t k_atoms = (k / vec + 3) / 4;
+    const int64_t tiles = ((rows + 127) / 128) * k_atoms;
+    return encode_2d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, p, 128, static_cast<uint64_t>(tiles), 512, 128, box_tiles,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, what);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ----------------------------------------------------------------------------------
+template <int CG, int BN, int VEC, int ST, int ACC>
+int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
+                const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream) {
+    using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    int rc;
+    if ((rc = encode_packed(&tm_a, a, m, k, 128, "A"))) return rc;
+    if ((rc = encode_packed(&tm_b, b, n, k, Cfg::kBnCta, "B"))) return rc;
+    if ((rc = encode_sf(&tm_sfa, sfa, m, k, VEC, Cfg::kSfK, "A scales"))) return rc;
+    if ((rc = encode_sf(&tm_sfb, sfb, n, k, VEC, Cfg::kSfK, "B scales"))) return rc;
+    if ((rc = encode_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d, static_cast<uint64_t>(n), static_cast<uint64_t>(m),
+                        static_cast<uint64_t>(ldd) * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, "D")))
+        return rc;
+
+    GemmParams p;
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.tiles_m = static_cast<int>((m + 128 * CG - 1) / (128 * CG));
+    p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+    p.sf_k_atoms = static_cast<int>((k / VEC + 3) / 4);
+    p.a_gs = ags;
+    p.b_gs = bgs;
+    p.status = ds.status;
+
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    long long clusters = ds.sm_count / CG;
+    if (tiles < clusters) clusters = tiles;
+
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * CG), 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p));
+    return 0;
+}
+
+int skinny_mp(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
+
+int64_t skinny_counter_bytes(int64_t n) {
+    const int64_t tiles_n = (n + 127) / 128;
+    return ((tiles_n * 4 * 4 + 255) / 256) * 256;
+}
+
+int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
+    return skinny_counter_bytes(n) + static_cast<int64_t>(sm_count) * 2 * skinny_mp(m) * 128 * 4;
+}
+
+template <int MP, int VEC, int ST>
+int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const float* xgs, const void* w, const void* sfw,
+                  const float* wgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, void* workspace,
+                  cudaStream_t stream) {
+    using Cfg = SkinnyConfig<MP, VEC, ST>;
+    CUtensorMap tm_w, tm_x, tm_sfw, tm_sfx;
+    int rc;
+    if ((rc = encode_packed(&tm_w, w, n, k, 128, "B"))) return rc;
+    if ((rc = encode_packed(&tm_x, x, m, k, MP, "A"))) return rc;
+    if ((rc = encode_sf(&tm_sfw, sfw, n, k, VEC, Cfg::kSfK, "B scales"))) return rc;
+    if ((rc = encode_sf(&tm_sfx, sfx, m, k, VEC, Cfg::kSfK, "A scales"))) return rc;
+
+    SkinnyParams p;
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.tiles_n = static_cast<int>((n + 127) / 128);
+    p.w_sf_k_atoms = static_cast<int>((k / VEC + 3) / 4);
+    p.ldd = static_cast<int>(ldd);
+    p.x_gs = xgs;
+    p.w_gs = wgs;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + skinny_counter_bytes(n));
+    p.status = ds.status;
+
+    const long long units = static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
+    long long grid = ds.sm_count;
+    if (units < grid) grid = units;
+    gemm_fp4_skinny_kernel<MP, VEC, ST><<<static_cast<unsigned>(grid), 192, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_sfw,
+                                                                                                      tm_sfx, p);
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int resolve_variant(int variant, int64_t m, int64_t n) {
+    if (variant != AVE_FP4_GEMM_AUTO) return variant;
+    if (m <= 64) return AVE_FP4_GEMM_SKINNY;
+    (void)n;
+    return AVE_FP4_GEMM_2CTA_N256;
+}
+
+}  // namespace
+
+// ====================================================================================
+extern "C" {
+
+const char* ave_fp4_last_error(void) { return g_err; }
+
+int ave_fp4_init(int device) {
+    if (device < 0 || device >= kMaxDevices) return fail(-AVE_FP4_ERR_ARG, "device %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_dev[device].ready) return 0;
+    int prev = -1;
+    AVE_CUDA(cudaGetDevice(&prev));
+    AVE_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    AVE_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        cudaSetDevice(prev);
+        return fail(-AVE_FP4_ERR_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                    prop.minor);
+    }
+    if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        AVE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (fn == nullptr || q != cudaDriverEntryPointSuccess) {
+            cudaSetDevice(prev);
+            return fail(-AVE_FP4_ERR_DEVICE, "driver does not export cuTensorMapEncodeTiled");
+        }
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    AVE_CUDA(prepare_all());
+    int* status = nullptr;
+    AVE_CUDA(cudaMalloc(&status, sizeof(int)));
+    AVE_CUDA(cudaMemset(status, 0, sizeof(int)));
+    g_dev[device].status = status;
+    g_dev[device].sm_count = prop.multiProcessorCount;
+    g_dev[device].ready = true;
+    AVE_CUDA(cudaSetDevice(prev));
+    return 0;
+}
+
+int ave_fp4_sm_count(void) {
+    DeviceState* ds = nullptr;
+    if (current_state(&ds)) return 0;
+    return ds->sm_count;
+}
+
+int64_t ave_fp4_sf_bytes(int64_t rows, int64_t k, int fmt, int sf_layout) {
+    const int64_t blk = (fmt == AVE_FP4_FMT_NVFP4) ? 16 : 32;
+    const int64_t cols = k / blk;
+    if (sf_layout == AVE_FP4_SF_ROW_MAJOR) return rows * cols;
+    return ((rows + 127) / 128) * ((cols + 3) / 4) * 512;
+}
+
+int64_t ave_fp4_workspace_bytes(int64_t m, int64_t n, int64_t k, int fmt, int variant, int device) {
+    (void)k;
+    (void)fmt;
+    if (resolve_variant(variant, m, n) != AVE_FP4_GEMM_SKINNY) return 0;
+    if (device < 0 || device >= kMaxDevices || !g_dev[device].ready) return -AVE_FP4_ERR_NOT_INIT;
+    return skinny_workspace_bytes(m, n, g_dev[device].sm_count);
+}
+
+int ave_fp4_amax(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void* amax_f32, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (!x_bf16 || !amax_f32 || rows < 0 || k < 0 || k % 8 != 0 || ldx % 8 != 0 || !aligned16(x_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_amax: need k %% 8 == 0, ldx %% 8 == 0 and a 16-byte aligned input");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    AVE_CUDA(cudaMemsetAsync(amax_f32, 0, 4, s));
+    const long long groups = rows * (k / 8);
+    if (groups == 0) return 0;
+    long long blocks = (groups + 255) / 256;
+    const long long cap = static_cast<long long>(ds->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    amax_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), rows, k, ldx,
+                                                                   static_cast<unsigned int*>(amax_f32));
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, int fmt, const void* amax_f32,
+                     void* global_scale, void* packed, void* scales, int sf_layout, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
+    if (sf_layout != AVE_FP4_SF_ROW_MAJOR && sf_layout != AVE_FP4_SF_TILED)
+        return fail(-AVE_FP4_ERR_ARG, "unknown scale layout %d", sf_layout);
+    if (rows < 0 || k < 0 || k % 32 != 0 || ldx % 8 != 0 || ldx < k)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: need k %% 32 == 0 and ldx %% 8 == 0, ldx >= k (k=%lld ldx=%lld)",
+                    static_cast<long long>(k), static_cast<long long>(ldx));
+    if (rows == 0 || k == 0) return 0;
+    if (!x_bf16 || !packed || !scales || !aligned16(x_bf16) || !aligned16(packed))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: null or misaligned pointer");
+    if (fmt == AVE_FP4_FMT_NVFP4 && !global_scale)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: NVFP4 needs a global_scale pointer");
+    if (sf_layout == AVE_FP4_SF_TILED && (reinterpret_cast<uintptr_t>(scales) & 3u))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: tiled scales must be 4-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tiled = (sf_layout == AVE_FP4_SF_TILED);
+    const long long rows_pad = tiled ? ((rows + 127) / 128) * 128 : rows;
+    const long long items = rows_pad * ((k + 1023) / 1024);  // one warp step each
+    long long blocks = (items + 7) / 8;
+    const long long cap = static_cast<long long>(ds->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(x_bf16);
+    const unsigned int* amax = static_cast<const unsigned int*>(amax_f32);
+    float* gs = static_cast<float*>(global_scale);
+    uint8_t* pk = static_cast<uint8_t*>(packed);
+    uint8_t* sf = static_cast<uint8_t*>(scales);
+    const unsigned g = static_cast<unsigned>(blocks);
+    if (fmt == AVE_FP4_FMT_NVFP4) {
+        if (tiled) quantize_fp4_kernel<kFmtNvfp4, true><<<g, 256, 0, s>>>(x, rows, k, ldx, amax, gs, pk, sf);
+        else quantize_fp4_kernel<kFmtNvfp4, false><<<g, 256, 0, s>>>(x, rows, k, ldx, amax, gs, pk, sf);
+    } else {
+        if (tiled) quantize_fp4_kernel<kFmtMxfp4, true><<<g, 256, 0, s>>>(x, rows, k, ldx, nullptr, nullptr, pk, sf);
+        else quantize_fp4_kernel<kFmtMxfp4, false><<<g, 256, 0, s>>>(x, rows, k, ldx, nullptr, nullptr, pk, sf);
+    }
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, void* sf_tiled, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (rows < 0 || cols < 0) return fail(-AVE_FP4_ERR_ARG, "negative size");
+    if (rows == 0 || cols == 0) return 0;
+    if (!sf_row_major || !sf_tiled || (reinterpret_cast<uintptr_t>(sf_tiled) & 3u))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_sf_to_tiled: null or misaligned pointer");
+    const long long total = ((rows + 127) / 128) * 128 * ((cols + 3) / 4);
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(ds->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    sf_to_tiled_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(sf_row_major), rows, cols, static_cast<uint8_t*>(sf_tiled));
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                 const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                 int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
+    if (m < 0 || n < 0 || k < 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: size out of range");
+    if (m == 0 || n == 0) return 0;
+    if (k == 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
+    if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: ldd must be >= N and a multiple of 8, got %lld", static_cast<long long>(ldd));
+    if (!a_packed || !a_scales || !b_packed || !b_scales || !d_bf16 || !aligned16(a_packed) || !aligned16(a_scales) ||
+        !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: null or misaligned (16-byte) pointer");
+    const float* ags = static_cast<const float*>(a_global_scale);
+    const float* bgs = static_cast<const float*>(b_global_scale);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int v = resolve_variant(variant, m, n);
+    const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
+
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s
+    switch (v) {
+        case AVE_FP4_GEMM_1CTA_N128:
+            return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
+        case AVE_FP4_GEMM_1CTA_N256:
+            return nv ? launch_gemm<1, 256, 16, kSt1N256, 1>(GEMM_ARGS) : launch_gemm<1, 256, 32, kSt1N256, 1>(GEMM_ARGS);
+        case AVE_FP4_GEMM_2CTA_N256:
+            return nv ? launch_gemm<2, 256, 16, kSt2N256, 1>(GEMM_ARGS) : launch_gemm<2, 256, 32, kSt2N256, 1>(GEMM_ARGS);
+        case AVE_FP4_GEMM_2CTA_N128:
+            return nv ? launch_gemm<2, 128, 16, kSt2N128, 2>(GEMM_ARGS) : launch_gemm<2, 128, 32, kSt2N128, 2>(GEMM_ARGS);
+        case AVE_FP4_GEMM_SKINNY: {
+            if (m > 64) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: the skinny variant needs M <= 64, got %lld", static_cast<long long>(m));
+            const int64_t need = skinny_workspace_bytes(m, n, ds->sm_count);
+            if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+                return fail(-AVE_FP4_ERR_WORKSPACE, "ave_fp4_gemm: workspace of %lld bytes (256-byte aligned, zero-initialised) required, got %lld",
+                            static_cast<long long>(need), static_cast<long long>(workspace ? workspace_bytes : 0));
+#define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, s
+            const int mp = skinny_mp(m);
+            if (mp == 16) return nv ? launch_skinny<16, 16, kStSkinny16>(SKINNY_ARGS) : launch_skinny<16, 32, kStSkinny16>(SKINNY_ARGS);
+            if (mp == 32) return nv ? launch_skinny<32, 16, kStSkinny32>(SKINNY_ARGS) : launch_skinny<32, 32, kStSkinny32>(SKINNY_ARGS);
+            return nv ? launch_skinny<64, 16, kStSkinny64>(SKINNY_ARGS) : launch_skinny<64, 32, kStSkinny64>(SKINNY_ARGS);
+#undef SKINNY_ARGS
+        }
+        default:
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: unknown variant %d", variant);
+    }
+#undef GEMM_ARGS
+}
+
+int ave_fp4_check(void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    AVE_CUDA(cudaStreamSynchronize(s));
+    int status = 0;
+    AVE_CUDA(cudaMemcpy(&status, ds->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        AVE_CUDA(cudaMemset(ds->status, 0, sizeof(int)));
+        return fail(status, "ave-lang Error [CUDA]: a kernel gave up waiting (status %d: 101 producer, 102 MMA issuer, 103 epilogue)", status);
+    }
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,296 @@
+// Skinny (decode-shaped) block-scaled FP4 GEMM for sm_100a:
+//   D[M,N] (bf16) = alpha * X[M,K] * W[N,K]^T   with M <= MP <= 64.
+//
+// The weight matrix streams from HBM once, so the kernel is bandwidth-bound.  The
+// operands are swapped on the tensor core: 128 weight rows sit on the MMA M axis
+// (TMEM lanes) and the few activation rows on the MMA N axis (TMEM columns), so a
+// 128 x MP x 64 tcgen05.mma does the work without padding M up to 128.
+//
+// Work is split stream-K style: the (weight tile, K block) units are cut into
+// gridDim.x equal contiguous ranges, one per persistent CTA, so every SM pulls the
+// same number of bytes.  A range that covers only part of a tile's K writes an fp32
+// partial to scratch memory; the CTA that completes a tile last (per-tile arrival
+// counter) adds the partials in a fixed order and writes the bf16 result, so the
+// output is deterministic and nobody waits on another CTA.
+//
+// Plays the role of python/avelang_kernels/amdgpu_gemm.py:349-455 for the shapes
+// the reference tile (128x128) cannot fill.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "gemm_fp4_sm100.cuh"
+
+namespace avefp4 {
+
+struct SkinnyParams {
+    int m, n, k;
+    int tiles_n;          // ceil(N / 128)
+    int w_sf_k_atoms;     // scale tiles along K
+    int ldd;              // row stride of D in elements
+    const float* x_gs;    // device fp32 tensor scales or nullptr
+    const float* w_gs;
+    __nv_bfloat16* d;
+    float* partials;      // gridDim.x * 2 * MP * 128 fp32
+    int* counters;        // 4 * tiles_n ints, zero on entry, zero again on exit
+    int* status;
+};
+
+template <int MP, int SF_VEC, int STAGES>
+struct SkinnyConfig {
+    static constexpr int kBlockK = 256;
+    static constexpr int kSfK = kBlockK / SF_VEC / 4;
+    static constexpr int kWBytes = 128 * 128;
+    static constexpr int kXBytes = MP * 128;
+    static constexpr int kSfBytes = kSfK * 512;
+    static constexpr int kStageBytes = kWBytes + kXBytes + 2 * kSfBytes;
+    static constexpr int kAccStages = 2;
+    static constexpr int kOffW = 0;
+    static constexpr int kOffX = kOffW + STAGES * kWBytes;
+    static constexpr int kOffSfw = kOffX + STAGES * kXBytes;
+    static constexpr int kOffSfx = kOffSfw + STAGES * kSfBytes;
+    static constexpr int kOffBar = kOffSfx + STAGES * kSfBytes;
+    static constexpr int kNumBars = 2 * STAGES + 2 * kAccStages;
+    static constexpr int kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr int kOffFlag = kOffTmemPtr + 8;
+    static constexpr int kSmemBytes = kOffFlag + 8 + 1024;
+    static constexpr int kTmemSfw = kAccStages * MP;
+    static constexpr int kTmemSfx = kTmemSfw + kSfK * 4;
+    static constexpr int kTmemUsed = kTmemSfx + kSfK * 4;
+    static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : 256;
+    static_assert(MP % 16 == 0 && MP >= 16 && MP <= 64, "MP must be 16, 32, 48 or 64");
+    static_assert((MP * 128) % 1024 == 0, "activation tile must keep 1024-byte alignment of later stages");
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+// CTA whose unit range [floor(i*U/G), floor((i+1)*U/G)) holds unit u.
+__device__ __forceinline__ int skinny_cta_of(long long u, long long units, long long ctas) {
+    return static_cast<int>(((u + 1) * ctas - 1) / units);
+}
+
+template <int MP, int SF_VEC, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                       const __grid_constant__ CUtensorMap tm_sfw, const __grid_constant__ CUtensorMap tm_sfx,
+                       const SkinnyParams p) {
+    using Cfg = SkinnyConfig<MP, SF_VEC, STAGES>;
+    constexpr int ACC = Cfg::kAccStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
+    const long long units = static_cast<long long>(p.tiles_n) * num_kb;
+    const long long ctas = gridDim.x;
+    const long long u_begin = (static_cast<long long>(blockIdx.x) * units) / ctas;
+    const long long u_end = (static_cast<long long>(blockIdx.x + 1) * units) / ctas;
+
+    const uint32_t bar_full = smem_base + Cfg::kOffBar;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_tfull = bar_empty + STAGES * 8;
+    const uint32_t bar_tempty = bar_tfull + ACC * 8;
+    const uint32_t tmem_ptr_smem = smem_base + Cfg::kOffTmemPtr;
+    volatile uint32_t* tmem_ptr_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kOffTmemPtr);
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_x);
+        prefetch_tensormap(&tm_sfw);
+        prefetch_tensormap(&tm_sfx);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < ACC; ++a) {
+            mbar_init(bar_tfull + a * 8, 1);
+            mbar_init(bar_tempty + a * 8, 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(tmem_ptr_smem, Cfg::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_gen;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long u = u_begin; u < u_end && ok; ++u) {
+                const int tile = static_cast<int>(u / num_kb);
+                const int kb = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
+                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+                    atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = bar_full + stage * 8;
+                mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+                tma_load_2d<1>(smem_base + Cfg::kOffW + stage * Cfg::kWBytes, &tm_w, full, kb * 128, tile * 128);
+                tma_load_2d<1>(smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes, &tm_sfw, full, 0,
+                               tile * p.w_sf_k_atoms + kb * Cfg::kSfK);
+                tma_load_2d<1>(smem_base + Cfg::kOffX + stage * Cfg::kXBytes, &tm_x, full, kb * 128, 0);
+                tma_load_2d<1>(smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes, &tm_sfx, full, 0, kb * Cfg::kSfK);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) {
+                for (int i = 0; i < STAGES; ++i) {
+                    if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        break;
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr bool kUe8m0 = (SF_VEC == 32);
+            int stage = 0;
+            uint32_t phase = 0;
+            int seg = 0;
+            bool ok = true;
+            for (long long u = u_begin; u < u_end && ok; ++seg) {
+                const int kb0 = static_cast<int>(u % num_kb);
+                const long long left = u_end - u;
+                const int kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
+                const int acc = seg % ACC;
+                const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
+                if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
+                    atomicCAS(p.status, 0, kStatusTimeoutMma);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * MP;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(bar_full + stage * 8, phase)) {
+                        atomicCAS(p.status, 0, kStatusTimeoutMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sfw_s = smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes;
+                    const uint32_t sfx_s = smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes;
+#pragma unroll
+                    for (int j = 0; j < Cfg::kSfK; ++j) {
+                        tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfw + j * 4, make_desc_sf(sfw_s + j * 512));
+                        tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfx + j * 4, make_desc_sf(sfx_s + j * 512));
+                    }
+                    const uint64_t w_desc = make_desc_k_sw128(smem_base + Cfg::kOffW + stage * Cfg::kWBytes);
+                    const uint64_t x_desc = make_desc_k_sw128(smem_base + Cfg::kOffX + stage * Cfg::kXBytes);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int sf_tile = (SF_VEC == 16) ? j : (j >> 1);
+                        const int sf_id = (SF_VEC == 16) ? 0 : 2 * (j & 1);
+                        const uint32_t idesc = make_idesc_fp4(128, MP, kUe8m0, sf_id);
+                        mma_fp4_block_scaled<1, SF_VEC>(d_tmem, w_desc + static_cast<uint64_t>(j * 2),
+                                                        x_desc + static_cast<uint64_t>(j * 2), idesc,
+                                                        tmem_base + Cfg::kTmemSfw + sf_tile * 4,
+                                                        tmem_base + Cfg::kTmemSfx + sf_tile * 4,
+                                                        (kb > kb0 || j > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit<1>(bar_empty + stage * 8);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tcgen05_commit<1>(bar_tfull + acc * 8);
+                u += kb1 - kb0;
+            }
+        }
+    } else {
+        // --------------------------------------------------------------- epilogue
+        const int quad = warp & 3;
+        const int n_local = quad * 32 + lane;
+        float alpha = 1.0f;
+        if (p.x_gs) alpha *= __ldg(p.x_gs);
+        if (p.w_gs) alpha *= __ldg(p.w_gs);
+        int seg = 0;
+        bool ok = true;
+        for (long long u = u_begin; u < u_end && ok; ++seg) {
+            const int tile = static_cast<int>(u / num_kb);
+            const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
+            const long long left = u_end - u;
+            const int kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
+            u += kb1 - kb0;
+            const int acc = seg % ACC;
+            const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
+            if (!mbar_wait(bar_tfull + acc * 8, acc_phase)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * MP;
+            uint32_t v[MP];
+#pragma unroll
+            for (int c = 0; c < MP / 16; ++c)
+                tmem_ld_32x32b_x16(t_acc + c * 16, reinterpret_cast<uint32_t(&)[16]>(v[c * 16]));
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + acc * 8);
+
+            const int n = tile * 128 + n_local;
+            const bool whole = (kb0 == 0 && kb1 == num_kb);
+            if (whole) {
+                if (n < p.n) {
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(__uint_as_float(v[m]) * alpha);
+                }
+            } else {
+                const int slot = (kb0 == 0) ? 1 : 0;
+                float* mine = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MP * 128);
+#pragma unroll
+                for (int m = 0; m < MP; ++m) __stcg(mine + m * 128 + n_local, __uint_as_float(v[m]));
+                // Each warp owns 32 weight rows of the tile and settles them on its own
+                // (counter per tile and warp quadrant), so no barrier between warps is needed.
+                __threadfence();
+                __syncwarp();
+                int f = -1;
+                if (lane == 0) {
+                    const int c0 = skinny_cta_of(static_cast<long long>(tile) * num_kb, units, ctas);
+                    const int c1 = skinny_cta_of(static_cast<long long>(tile + 1) * num_kb - 1, units, ctas);
+                    const int old = atomicAdd(p.counters + tile * 4 + quad, 1);
+                    if (old == c1 - c0) {
+                        p.counters[tile * 4 + quad] = 0;
+                        f = c0 | (c1 << 16);
+                    }
+                }
+                f = __shfl_sync(0xffffffffu, f, 0);
+                if (f >= 0) {
+                    __threadfence();
+                    const int c0 = f & 0xffff, c1 = f >> 16;
+                    float sum[MP];
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) sum[m] = 0.0f;
+                    for (int c = c0; c <= c1; ++c) {
+                        const float* src = p.partials + (static_cast<size_t>(c) * 2 + (c == c0 ? 1 : 0)) * (MP * 128);
+#pragma unroll
+                        for (int m = 0; m < MP; ++m) sum[m] += __ldcg(src + m * 128 + n_local);
+                    }
+                    if (n < p.n) {
+#pragma unroll
+                        for (int m = 0; m < MP; ++m)
+                            if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(sum[m] * alpha);
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+}
+
+}  // namespace avefp4

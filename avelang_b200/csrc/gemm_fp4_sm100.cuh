@@ -1,0 +1,328 @@
+// Block-scaled FP4 GEMM  D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T  for sm_100a.
+//
+// Counterpart of the reference operator kernel
+// python/avelang_kernels/amdgpu_gemm.py:349-455 (one 128x128 tile per workgroup,
+// LDS-staged MFMA loop, bf16 truncating store) re-designed for Blackwell:
+//
+//   * persistent CTAs (optionally 2-CTA pairs), static tile schedule with grouped raster;
+//   * warp 0: TMA producer -- packed E2M1 tiles (128-byte swizzle, 256 K-elements per
+//     row chunk) and 128x4 scale-factor tiles into a STAGES-deep shared-memory ring;
+//   * warp 1: one thread issues tcgen05.cp (scale factors smem -> TMEM) and
+//     tcgen05.mma kind::mxf4nvf4 / kind::mxf4 block-scaled, fp32 accumulators in TMEM;
+//   * warps 2-5: epilogue -- tcgen05.ld, * alpha, round-to-nearest-even bf16,
+//     swizzled shared-memory staging, TMA store (coalesced 128-byte rows, clipped at
+//     the matrix edges).
+//
+// Operand convention (python/avelang_kernels/amdgpu_gemm.py:458-494): A is (M,K),
+// B is (N,K), both K-contiguous; D = A * B^T.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "sm100_ptx.cuh"
+
+namespace avefp4 {
+
+enum GemmStatus : int {
+    kStatusOk = 0,
+    kStatusTimeoutProducer = 101,
+    kStatusTimeoutMma = 102,
+    kStatusTimeoutEpilogue = 103,
+};
+
+struct GemmParams {
+    int m, n, k;
+    int tiles_m, tiles_n;      // in units of (128 * CTA_GROUP) x BLOCK_N
+    int sf_k_atoms;            // 128x4 scale tiles along K: ceil(K / SF_VEC / 4)
+    const float* a_gs;         // device fp32 scalars (NVFP4 tensor scales) or nullptr
+    const float* b_gs;
+    int* status;               // device status word, written on a wait timeout
+};
+
+template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
+struct GemmConfig {
+    static constexpr int kBlockM = 128;                 // rows of A per CTA
+    static constexpr int kBlockK = 256;                 // K elements per stage = 128 bytes
+    static constexpr int kBnCta = BLOCK_N / CTA_GROUP;  // rows of B loaded by one CTA
+    static constexpr int kNb = BLOCK_N / 128;           // 128-row scale tiles across BLOCK_N
+    static constexpr int kSfK = kBlockK / SF_VEC / 4;   // scale tiles along K per stage (4 NVFP4, 2 MXFP4)
+    static constexpr int kABytes = kBlockM * 128;
+    static constexpr int kBBytes = kBnCta * 128;
+    static constexpr int kSfaBytes = kSfK * 512;
+    static constexpr int kSfbBytes = kNb * kSfK * 512;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr uint32_t kTxBytes = static_cast<uint32_t>(kStageBytes) * CTA_GROUP;
+    static constexpr int kEpiBufs = 2;
+    static constexpr int kEpiBufBytes = 32 * 128;       // 32 rows x 64 bf16
+    static constexpr int kEpiBytes = 4 * kEpiBufs * kEpiBufBytes;
+    static constexpr int kOffA = 0;
+    static constexpr int kOffB = kOffA + STAGES * kABytes;
+    static constexpr int kOffSfa = kOffB + STAGES * kBBytes;
+    static constexpr int kOffSfb = kOffSfa + STAGES * kSfaBytes;
+    static constexpr int kOffEpi = kOffSfb + STAGES * kSfbBytes;
+    static constexpr int kOffBar = kOffEpi + kEpiBytes;
+    static constexpr int kNumBars = 2 * STAGES + 2 * ACC_STAGES;
+    static constexpr int kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr int kSmemBytes = kOffTmemPtr + 16 + 1024;  // + slack for 1024-byte alignment
+    static constexpr int kTmemAcc = 0;
+    static constexpr int kTmemSfa = ACC_STAGES * BLOCK_N;
+    static constexpr int kTmemSfb = kTmemSfa + kSfK * 4;
+    static constexpr int kTmemUsed = kTmemSfb + kSfK * kNb * 4;
+    static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : kTmemUsed <= 256 ? 256 : 512;
+    static constexpr int kThreads = 192;
+    static_assert(BLOCK_N % 128 == 0 && BLOCK_N <= 256, "BLOCK_N must be 128 or 256");
+    static_assert(kTmemUsed <= 512, "tensor memory budget");
+    static_assert(kOffB % 1024 == 0 && kOffSfa % 1024 == 0 && kOffEpi % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+// Tile index -> (tile_m, tile_n): bands of 8 tile rows, M fastest inside a band, so
+// concurrently running CTAs share a few A panels and a few B panels in L2.
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    constexpr int kGroup = 8;
+    const int band = kGroup * tiles_n;
+    const int g = t / band;
+    const int first = g * kGroup;
+    const int gm = min(tiles_m - first, kGroup);
+    const int r = t - g * band;
+    tm = first + r % gm;
+    tn = r / gm;
+}
+
+template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+                const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
+    using Cfg = GemmConfig<CTA_GROUP, BLOCK_N, SF_VEC, STAGES, ACC_STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTA_GROUP == 2) ? cluster_ctarank() : 0u;
+    const bool is_leader = (cta_rank == 0);
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int num_clusters = gridDim.x / CTA_GROUP;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
+
+    const uint32_t bar_full = smem_base + Cfg::kOffBar;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_tfull = bar_empty + STAGES * 8;
+    const uint32_t bar_tempty = bar_tfull + ACC_STAGES * 8;
+    const uint32_t tmem_ptr_smem = smem_base + Cfg::kOffTmemPtr;
+    volatile uint32_t* tmem_ptr_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kOffTmemPtr);
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_sfa);
+        prefetch_tensormap(&tm_sfb);
+        prefetch_tensormap(&tm_d);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(bar_tfull + a * 8, 1);
+            mbar_init(bar_tempty + a * 8, 4 * CTA_GROUP);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<CTA_GROUP>(tmem_ptr_smem, Cfg::kTmemCols);
+        tmem_relinquish<CTA_GROUP>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_gen;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint32_t full0 = (CTA_GROUP == 2) ? mapa_shared(bar_full, 0) : bar_full;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                int tm, tn;
+                decode_tile(t, p.tiles_m, p.tiles_n, tm, tn);
+                const int row_a = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM;
+                const int row_b = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBnCta;
+                const int sfa_atom0 = (row_a / 128) * p.sf_k_atoms;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = full0 + stage * 8;
+                    if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
+                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
+                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
+                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
+                                           sfa_atom0 + kb * Cfg::kSfK);
+#pragma unroll
+                    for (int nb = 0; nb < Cfg::kNb; ++nb) {
+                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
+                                               &tm_sfb, full, 0,
+                                               (tn * Cfg::kNb + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {
+                // Drain: wait until every stage this CTA filled has been consumed, so no
+                // copy is in flight and no peer signal is outstanding when the CTA exits.
+                for (int i = 0; i < STAGES; ++i) {
+                    if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        break;
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0 && is_leader) {
+            constexpr int kMmaM = 128 * CTA_GROUP;
+            constexpr bool kUe8m0 = (SF_VEC == 32);
+            int stage = 0;
+            uint32_t phase = 0;
+            int tile_iter = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_iter) {
+                const int acc = tile_iter % ACC_STAGES;
+                const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
+                if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
+                    atomicCAS(p.status, 0, kStatusTimeoutMma);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + Cfg::kTmemAcc + acc * BLOCK_N;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(bar_full + stage * 8, phase)) {
+                        atomicCAS(p.status, 0, kStatusTimeoutMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sfa_s = smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes;
+                    const uint32_t sfb_s = smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes;
+#pragma unroll
+                    for (int j = 0; j < Cfg::kSfK; ++j) {
+                        tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfa + j * 4, make_desc_sf(sfa_s + j * 512));
+#pragma unroll
+                        for (int nb = 0; nb < Cfg::kNb; ++nb)
+                            tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfb + (j * Cfg::kNb + nb) * 4,
+                                                  make_desc_sf(sfb_s + (nb * Cfg::kSfK + j) * 512));
+                    }
+                    const uint64_t a_desc = make_desc_k_sw128(smem_base + Cfg::kOffA + stage * Cfg::kABytes);
+                    const uint64_t b_desc = make_desc_k_sw128(smem_base + Cfg::kOffB + stage * Cfg::kBBytes);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // one K=64 step = 32 bytes along the swizzled 128-byte row
+                        const int sf_tile = (SF_VEC == 16) ? j : (j >> 1);
+                        const int sf_id = (SF_VEC == 16) ? 0 : 2 * (j & 1);
+                        const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
+                        mma_fp4_block_scaled<CTA_GROUP, SF_VEC>(
+                            d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
+                            tmem_base + Cfg::kTmemSfa + sf_tile * 4, tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4,
+                            (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tcgen05_commit<CTA_GROUP>(bar_tfull + acc * 8);
+            }
+        }
+    } else {
+        // --------------------------------------------------------------- epilogue
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+        const uint32_t stage_buf = smem_base + Cfg::kOffEpi + (warp - 2) * Cfg::kEpiBufs * Cfg::kEpiBufBytes;
+        float alpha = 1.0f;
+        if (p.a_gs) alpha *= __ldg(p.a_gs);
+        if (p.b_gs) alpha *= __ldg(p.b_gs);
+        const uint32_t tempty0 = (CTA_GROUP == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
+        int tile_iter = 0;
+        int buf = 0;
+        bool ok = true;
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_iter) {
+            int tm, tn;
+            decode_tile(t, p.tiles_m, p.tiles_n, tm, tn);
+            const int acc = tile_iter % ACC_STAGES;
+            const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
+            if (!mbar_wait(bar_tfull + acc * 8, acc_phase)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM + quad * 32;
+            const int col0 = tn * BLOCK_N;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N;
+            constexpr int kChunks = BLOCK_N / 64;
+            uint32_t v[2][64];
+            tmem_ld_32x32b_x32(t_acc, reinterpret_cast<uint32_t(&)[32]>(v[0][0]));
+            tmem_ld_32x32b_x32(t_acc + 32, reinterpret_cast<uint32_t(&)[32]>(v[0][32]));
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                tmem_ld_wait();
+                if (c + 1 < kChunks) {
+                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 64, reinterpret_cast<uint32_t(&)[32]>(v[(c + 1) & 1][0]));
+                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[(c + 1) & 1][32]));
+                } else {
+                    // all accumulator columns of this tile are in registers: hand TMEM back
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(tempty0 + acc * 8);
+                        else mbar_arrive(bar_tempty + acc * 8);
+                    }
+                }
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float lo = __uint_as_float(v[c & 1][2 * i]) * alpha;
+                    const float hi = __uint_as_float(v[c & 1][2 * i + 1]) * alpha;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                // staging buffer `buf` may still be read by the TMA store issued two chunks ago
+                if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+                __syncwarp();
+                const uint32_t sbuf = stage_buf + buf * Cfg::kEpiBufBytes;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    // 128-byte swizzle: 16-byte chunk q of row `lane` lives at chunk q ^ (lane & 7)
+                    const uint32_t addr = sbuf + lane * 128 + ((q ^ (lane & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]),
+                                 "r"(packed[4 * q + 1]), "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
+                                 : "memory");
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tm_d, sbuf, col0 + c * 64, row0);
+                    tma_store_commit();
+                }
+                buf ^= 1;
+            }
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) cluster_sync_all();
+    if (warp == 1) tmem_dealloc<CTA_GROUP>(tmem_base, Cfg::kTmemCols);
+}
+
+}  // namespace avefp4

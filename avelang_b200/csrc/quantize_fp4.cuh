@@ -1,0 +1,213 @@
+// bf16 -> NVFP4 / MXFP4 quantise kernels (bandwidth-bound).
+//
+// The reference has no quantise operator; its only quantise-like primitive is the
+// packed fp8 conversion python/avelang/language/amdgpu.py:90-94.  The arithmetic
+// here is, operation for operation, the CPU oracle's (oracle/fp4_oracle.c): every
+// fp32 step is a single round-to-nearest-even operation (explicit _rn intrinsics,
+// IEEE division), so packed nibbles and scale bytes are bit-identical.
+//
+// Mapping: a warp takes 1024 consecutive K elements of one row per step.  Lane L
+// loads four 128-bit groups (elements 8*(32*j+L) .. +7, j = 0..3), so every load
+// instruction of the warp is one contiguous 512-byte run.  The block maximum is
+// formed with warp shuffles (2 lanes per 16-element NVFP4 block, 4 lanes per
+// 32-element MXFP4 block).  Each lane packs its 8 values into one 32-bit word; a
+// 4x4 exchange inside each lane quad then gives every lane 16 contiguous output
+// bytes, written with one 128-bit store.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include <cstdint>
+
+namespace avefp4 {
+
+constexpr int kFmtNvfp4 = 0;
+constexpr int kFmtMxfp4 = 1;
+constexpr int kSfRowMajor = 0;
+constexpr int kSfTiled = 1;
+
+// max |x| over a (rows, k) bf16 matrix with row stride ldx; result = fp32 bit pattern
+// in *amax_bits (must be zero on entry; non-negative floats order like unsigned ints).
+__global__ void __launch_bounds__(256)
+amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
+                 unsigned int* __restrict__ amax_bits) {
+    const long long groups_per_row = k / 8;
+    const long long total = rows * groups_per_row;
+    float a = 0.0f;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < total;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = g / groups_per_row;
+        const long long c = g - r * groups_per_row;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + c * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            a = fmaxf(a, fabsf(__uint_as_float(w[i] << 16)));
+            a = fmaxf(a, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if ((threadIdx.x & 31) == 0 && a > 0.0f) atomicMax(amax_bits, __float_as_uint(a));
+}
+
+__device__ __forceinline__ float e4m3_decode(uint32_t c) {
+    const uint32_t e = (c >> 3) & 0xfu, m = c & 7u;
+    if (e == 0) return static_cast<float>(m) * 0.001953125f;  // m * 2^-9, exact
+    return __uint_as_float(((e + 120u) << 23) | (m << 20));
+}
+
+// Offset of scale (row r, scale column c) in the 128x4 tiled layout with `k_atoms` tiles along K.
+__device__ __forceinline__ long long sf_tiled_offset(long long r, long long c, long long k_atoms) {
+    const long long rr = r & 127;
+    return ((r >> 7) * k_atoms + (c >> 2)) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (c & 3);
+}
+
+// Pack 8 floats (already divided by the block scale) into 8 E2M1 nibbles, element i in nibble i.
+__device__ __forceinline__ uint32_t pack8_e2m1(const float (&y)[8]) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_fp4x2_storage_t b = __nv_cvt_float2_to_fp4x2(make_float2(y[2 * i], y[2 * i + 1]), __NV_E2M1, cudaRoundNearest);
+        w |= static_cast<uint32_t>(b) << (8 * i);
+    }
+    return w;
+}
+
+// FMT: kFmtNvfp4 (16-element blocks, E4M3 scale relative to the tensor scale gs) or
+// kFmtMxfp4 (32-element blocks, E8M0 scale).  TILED: scale bytes go to the 128x4 tiled
+// layout (rows padded to 128 and scale columns to 4, padding written as zero).
+//
+// amax_bits != nullptr: gs = amax / 2688 (1 when amax == 0), also stored to *gs_io.
+// amax_bits == nullptr: gs = *gs_io (caller-supplied static scale).
+template <int FMT, bool TILED>
+__global__ void __launch_bounds__(256)
+quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
+                    const unsigned int* __restrict__ amax_bits, float* __restrict__ gs_io,
+                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+    constexpr int BLK = (FMT == kFmtNvfp4) ? 16 : 32;
+    const int lane = threadIdx.x & 31;
+    const long long warp_global = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+
+    float gs = 1.0f;
+    if (FMT == kFmtNvfp4) {
+        if (amax_bits != nullptr) {
+            const float amax = __uint_as_float(*amax_bits);
+            gs = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 2688.0f);
+            if (blockIdx.x == 0 && threadIdx.x == 0) *gs_io = gs;
+        } else {
+            gs = *gs_io;
+        }
+    }
+
+    const long long sf_cols = k / BLK;
+    const long long k_atoms = (sf_cols + 3) / 4;
+    const long long rows_pad = TILED ? ((rows + 127) / 128) * 128 : rows;
+    const long long k_pad = TILED ? k_atoms * 4 * BLK : k;
+    const long long chunks = (k_pad + 1023) / 1024;
+    const long long items = rows_pad * chunks;
+    const int quad_base = lane & ~3;
+    const int qi = lane & 3;
+
+    for (long long item = warp_global; item < items; item += warps_total) {
+        const long long r = item / chunks;
+        const long long e0 = (item - r * chunks) * 1024;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long e = e0 + (j * 32 + lane) * 8;
+            const bool in = (r < rows) && (e < k);
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (in) raw = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + e));
+            const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(rw[i] << 16);
+                v[2 * i + 1] = __uint_as_float(rw[i] & 0xffff0000u);
+            }
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(v[i]));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            if (FMT == kFmtMxfp4) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+
+            uint32_t code;
+            float y[8];
+            if (FMT == kFmtNvfp4) {
+                const float t = __fdiv_rn(a, 6.0f);
+                const float u = fminf(__fdiv_rn(t, gs), 448.0f);
+                code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
+                const float d = __fmul_rn(e4m3_decode(code), gs);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = (d == 0.0f) ? copysignf(0.0f, v[i]) : __fdiv_rn(v[i], d);
+            } else {
+                if (a == 0.0f) {
+                    code = 127u;
+                } else {
+                    const int E = static_cast<int>((__float_as_uint(a) >> 23) & 0xffu);
+                    code = static_cast<uint32_t>(max(E - 2, 0));
+                }
+                const float inv = __uint_as_float((254u - code) << 23);  // 2^(127-code), exact scaling
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(v[i], inv);
+            }
+            w[j] = pack8_e2m1(y);
+
+            // scale byte: one lane per block writes it
+            const bool sf_writer = (FMT == kFmtNvfp4) ? ((lane & 1) == 0) : ((lane & 3) == 0);
+            if (sf_writer && e < k_pad) {
+                const long long c = e / BLK;
+                const uint8_t byte = in ? static_cast<uint8_t>(code) : static_cast<uint8_t>(0);
+                if (TILED) sf[sf_tiled_offset(r, c, k_atoms)] = byte;
+                else if (in) sf[r * sf_cols + c] = byte;
+            }
+        }
+        // 4x4 exchange inside each quad: lane q ends up with word q of all four lanes,
+        // i.e. the 16 contiguous output bytes of 32 consecutive elements of segment q.
+        uint32_t o[4];
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+            const int send_idx = (qi + rr) & 3;
+            const uint32_t send = send_idx == 0 ? w[0] : send_idx == 1 ? w[1] : send_idx == 2 ? w[2] : w[3];
+            const int src = (qi - rr) & 3;
+            const uint32_t got = __shfl_sync(0xffffffffu, send, quad_base + src);
+            // value received is word `qi` of lane `src`
+            if (src == 0) o[0] = got;
+            else if (src == 1) o[1] = got;
+            else if (src == 2) o[2] = got;
+            else o[3] = got;
+        }
+        const long long e_out = e0 + (qi * 32 + quad_base) * 8;  // first element of this lane's 32-element run
+        if (r < rows && e_out < k) {
+            *reinterpret_cast<uint4*>(packed + r * (k / 2) + e_out / 2) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// Row-major (rows, cols) scale bytes -> 128x4 tiled layout (padding zero).
+__global__ void __launch_bounds__(256)
+sf_to_tiled_kernel(const uint8_t* __restrict__ src, long long rows, long long cols, uint8_t* __restrict__ dst) {
+    const long long k_atoms = (cols + 3) / 4;
+    const long long rows_pad = ((rows + 127) / 128) * 128;
+    const long long total = rows_pad * k_atoms;  // one thread per (row, 4 scale columns)
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / k_atoms;
+        const long long a = i - r * k_atoms;
+        uint32_t word = 0;
+        if (r < rows) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const long long col = a * 4 + c;
+                if (col < cols) word |= static_cast<uint32_t>(src[r * cols + col]) << (8 * c);
+            }
+        }
+        *reinterpret_cast<uint32_t*>(dst + sf_tiled_offset(r, a * 4, k_atoms)) = word;
+    }
+}
+
+}  // namespace avefp4

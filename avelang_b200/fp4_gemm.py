@@ -1,0 +1,253 @@
+"""FP4 operators in the reference's operator convention.
+
+The reference ships one operator, ``gemm_pipeline_transposed_b(A, B, out=None) -> Tensor``
+(python/avelang_kernels/amdgpu_gemm.py:458-494): A is (M, K), B is (N, K), both
+K-contiguous, the result is ``A @ B.T`` with fp32 accumulation and bf16 output,
+arguments are validated with ``ValueError`` before anything is launched, ``out`` is
+allocated only when not given, and the launch is asynchronous on the current stream.
+
+The operators here keep that shape of API for block-scaled FP4 operands:
+
+* ``quantize_nvfp4(x, global_scale=None)`` / ``quantize_mxfp4(x)`` -> ``Fp4Operand``
+* ``gemm_nvfp4_transposed_b(A, B, out=None)`` / ``gemm_mxfp4_transposed_b(A, B, out=None)``
+
+All compute runs in hand-written CUDA kernels behind the C ABI of ``libavefp4.so``;
+torch tensors are used only to own device memory and to name the current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+NVFP4 = 0
+MXFP4 = 1
+SF_ROW_MAJOR = 0
+SF_TILED = 1
+
+GEMM_AUTO = 0
+GEMM_1CTA_N128 = 1
+GEMM_1CTA_N256 = 2
+GEMM_2CTA_N256 = 3
+GEMM_2CTA_N128 = 4
+GEMM_SKINNY = 10
+
+_BLOCK = {NVFP4: 16, MXFP4: 32}
+_FMT_NAME = {NVFP4: "NVFP4", MXFP4: "MXFP4"}
+
+
+@dataclass
+class Fp4Operand:
+    """A quantised (rows, k) matrix, K contiguous.
+
+    packed        uint8 (rows, k/2): element 2j in bits 3:0 of byte j, 2j+1 in bits 7:4 (E2M1)
+    scales        uint8, one per 16 (NVFP4, E4M3) or 32 (MXFP4, E8M0) K elements;
+                  (rows, k/blk) when ``sf_layout == SF_ROW_MAJOR``, flat 128x4 tiles when ``SF_TILED``
+    global_scale  fp32 tensor with one element on the same device (NVFP4) or None (MXFP4)
+    """
+
+    packed: torch.Tensor
+    scales: torch.Tensor
+    global_scale: torch.Tensor | None
+    fmt: int
+    rows: int
+    k: int
+    sf_layout: int = SF_TILED
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return (self.rows, self.k)
+
+    @property
+    def device(self) -> torch.device:
+        return self.packed.device
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    # the reference launches on torch's current raw stream (python/avelang/backends/driver.py:24-32)
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> int:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor, got device {t.device}.")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def sf_bytes(rows: int, k: int, fmt: int, sf_layout: int) -> int:
+    blk = _BLOCK[fmt]
+    cols = k // blk
+    if sf_layout == SF_ROW_MAJOR:
+        return rows * cols
+    return ((rows + 127) // 128) * ((cols + 3) // 4) * 512
+
+
+def _quantize(x: torch.Tensor, fmt: int, global_scale: torch.Tensor | None, sf_layout: int) -> Fp4Operand:
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"x must have dtype torch.bfloat16, got {x.dtype}.")
+    if x.dim() != 2:
+        raise ValueError(f"x must be 2-D (rows, K), got shape {tuple(x.shape)}.")
+    dev = _require_cuda(x, "x")
+    rows, k = x.shape
+    if k % 32 != 0:
+        raise ValueError(f"K must be a multiple of 32, got {k}.")
+    if x.stride(1) != 1 or (rows > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        raise ValueError("x must be K-contiguous with a 16-byte aligned row stride.")
+    if sf_layout not in (SF_ROW_MAJOR, SF_TILED):
+        raise ValueError(f"unknown scale layout {sf_layout}.")
+    ldx = x.stride(0) if rows > 1 else k
+    gs = None
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+        if sf_layout == SF_ROW_MAJOR:
+            scales = torch.empty((rows, k // _BLOCK[fmt]), dtype=torch.uint8, device=x.device)
+        else:
+            scales = torch.empty((sf_bytes(rows, k, fmt, SF_TILED),), dtype=torch.uint8, device=x.device)
+        stream = _stream(x.device)
+        amax = None
+        if fmt == NVFP4:
+            if global_scale is None:
+                amax = torch.empty((1,), dtype=torch.float32, device=x.device)
+                gs = torch.empty((1,), dtype=torch.float32, device=x.device)
+                _lib.check(L.ave_fp4_amax(_ptr(x), rows, k, ldx, _ptr(amax), stream))
+            else:
+                if global_scale.dtype != torch.float32 or global_scale.numel() != 1:
+                    raise ValueError("global_scale must be a float32 tensor with one element.")
+                if global_scale.device != x.device:
+                    raise ValueError(f"global_scale must be on device {x.device}, got {global_scale.device}.")
+                gs = global_scale.reshape(1)
+        elif global_scale is not None:
+            raise ValueError("MXFP4 has no global scale.")
+        _lib.check(L.ave_fp4_quantize(_ptr(x), rows, k, ldx, fmt, _ptr(amax), _ptr(gs), _ptr(packed), _ptr(scales),
+                                      sf_layout, stream))
+    return Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout)
+
+
+def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor | None = None, sf_layout: int = SF_TILED) -> Fp4Operand:
+    """bf16 (rows, K) -> NVFP4: 16-element blocks, E4M3 block scales, one fp32 tensor scale.
+
+    ``global_scale=None`` computes the tensor scale as amax / (6 * 448) on the device
+    (no host synchronisation); a given one-element fp32 tensor is used as a static scale.
+    """
+    return _quantize(x, NVFP4, global_scale, sf_layout)
+
+
+def quantize_mxfp4(x: torch.Tensor, sf_layout: int = SF_TILED) -> Fp4Operand:
+    """bf16 (rows, K) -> MXFP4: 32-element blocks, E8M0 (power of two) block scales."""
+    return _quantize(x, MXFP4, None, sf_layout)
+
+
+def to_tiled(op: Fp4Operand) -> Fp4Operand:
+    """Return ``op`` with its scales in the 128x4 tiled layout the GEMM consumes."""
+    if op.sf_layout == SF_TILED:
+        return op
+    dev = _require_cuda(op.scales, "scales")
+    cols = op.k // _BLOCK[op.fmt]
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        tiled = torch.empty((sf_bytes(op.rows, op.k, op.fmt, SF_TILED),), dtype=torch.uint8, device=op.scales.device)
+        _lib.check(L.ave_fp4_sf_to_tiled(_ptr(op.scales.contiguous()), op.rows, cols, _ptr(tiled), _stream(op.scales.device)))
+    return Fp4Operand(op.packed, tiled, op.global_scale, op.fmt, op.rows, op.k, SF_TILED)
+
+
+def make_operand(packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor | None, fmt: int,
+                 sf_layout: int = SF_ROW_MAJOR) -> Fp4Operand:
+    """Wrap tensors quantised elsewhere (e.g. offline weights) as an operand, checking shapes."""
+    if packed.dtype != torch.uint8 or packed.dim() != 2:
+        raise ValueError("packed must be a 2-D uint8 tensor (rows, K/2).")
+    rows, k = packed.shape[0], packed.shape[1] * 2
+    if scales.dtype != torch.uint8 or scales.numel() != sf_bytes(rows, k, fmt, sf_layout):
+        raise ValueError(f"scales must be uint8 with {sf_bytes(rows, k, fmt, sf_layout)} elements, got {scales.numel()}.")
+    return Fp4Operand(packed.contiguous(), scales.contiguous(), global_scale, fmt, rows, k, sf_layout)
+
+
+# One scratch buffer per device, shared by every call on that device: calls that could
+# overlap on the GPU (different streams) must not share it -- run them on one stream.
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _workspace(L, device: torch.device, dev: int, m: int, n: int, k: int, fmt: int, variant: int) -> torch.Tensor | None:
+    need = L.ave_fp4_workspace_bytes(m, n, k, fmt, variant, dev)
+    if need < 0:
+        raise RuntimeError(f"ave-lang Error [CUDA]: workspace query failed ({need}).")
+    if need == 0:
+        return None
+    key = dev
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        # zero-initialised once; the kernel leaves its counters at zero for the next call
+        ws = torch.zeros((need,), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int) -> torch.Tensor:
+    name = _FMT_NAME[fmt]
+    if A.fmt != fmt:
+        raise ValueError(f"A must be an {name} operand, got {_FMT_NAME.get(A.fmt, A.fmt)}.")
+    if B.fmt != fmt:
+        raise ValueError(f"B must be an {name} operand, got {_FMT_NAME.get(B.fmt, B.fmt)}.")
+    m, k = A.rows, A.k
+    n = B.rows
+    if B.k != k:
+        raise ValueError(f"A and B must share K, got {k} and {B.k}.")
+    if k % 32 != 0 or k == 0:
+        raise ValueError(f"K must be a positive multiple of 32, got {k}.")
+    if n % 8 != 0:
+        raise ValueError(f"N must be a multiple of 8, got {n}.")
+    dev = _require_cuda(A.packed, "A")
+    if B.device != A.device:
+        raise ValueError(f"B must be on device {A.device}, got {B.device}.")
+    if fmt == NVFP4 and (A.global_scale is None or B.global_scale is None):
+        raise ValueError("NVFP4 operands need a global_scale tensor.")
+    out_shape = (m, n)
+    if out is None:
+        out = torch.empty(out_shape, dtype=torch.bfloat16, device=A.device)
+    elif tuple(out.shape) != out_shape:
+        raise ValueError(f"out must have shape {out_shape}, got {tuple(out.shape)}.")
+    elif out.dtype != torch.bfloat16:
+        raise ValueError(f"out must have dtype torch.bfloat16, got {out.dtype}.")
+    elif out.device != A.device:
+        raise ValueError(f"out must be on device {A.device}, got {out.device}.")
+    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
+    if m == 0 or n == 0:
+        return out
+    A = to_tiled(A)
+    B = to_tiled(B)
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        ws = _workspace(L, A.device, dev, m, n, k, fmt, variant)
+        _lib.check(L.ave_fp4_gemm(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
+                                  _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt, variant, _ptr(ws),
+                                  0 if ws is None else ws.numel(), _stream(A.device)))
+    return out
+
+
+def gemm_nvfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
+                            variant: int = GEMM_AUTO) -> torch.Tensor:
+    """``out = A @ B.T`` for NVFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
+    return _gemm(A, B, out, NVFP4, variant)
+
+
+def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
+                            variant: int = GEMM_AUTO) -> torch.Tensor:
+    """``out = A @ B.T`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
+    return _gemm(A, B, out, MXFP4, variant)
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Synchronise the current stream and raise if a kernel recorded a wait time-out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        _lib.check(L.ave_fp4_check(_stream(device)))

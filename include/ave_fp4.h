@@ -1,0 +1,134 @@
+/*
+ * C ABI of libavefp4: block-scaled FP4 (NVFP4 / MXFP4) GEMM  D = A * B^T  and the
+ * bf16 -> FP4 activation quantise for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host binding talks to.  Plain pointers and sizes only; all
+ * pointers are device pointers unless stated otherwise; every call enqueues work on
+ * `stream` (a cudaStream_t passed as void*) of the current device and returns
+ * without synchronising, so calls are safe inside CUDA graph capture.  No entry
+ * point below allocates or frees device memory except ave_fp4_init.
+ *
+ * Return value: 0 on success; negative = argument error; positive = cudaError_t.
+ * ave_fp4_last_error() gives the message of the calling thread's last failure.
+ *
+ * Reference interfaces these entry points stand in for (paths inside
+ * causalflow-ai/avelang):
+ *   - the operator  gemm_pipeline_transposed_b(A, B, out=None)
+ *     python/avelang_kernels/amdgpu_gemm.py:458-494  (A (M,K), B (N,K), K contiguous,
+ *     D = A * B^T, fp32 accumulate, bf16 out);
+ *   - the launch convention of the NVIDIA backend: raw data_ptr() pointers, current
+ *     device, current raw stream, errors raised as RuntimeError
+ *     python/avelang/backends/nvidia/driver.py:68-81,120-131,284-311 and
+ *     python/avelang/backends/driver.py:24-32.
+ *
+ * Storage convention of a quantised (R,K) operand:
+ *   packed : uint8 (R, K/2) row-major; byte j = element 2j in bits 3:0, 2j+1 in bits 7:4;
+ *            a nibble is E2M1 (sign, 2 exponent bits, 1 mantissa bit).
+ *   scales : uint8; one per 16 (NVFP4, E4M3) or 32 (MXFP4, E8M0) consecutive K elements.
+ *            AVE_FP4_SF_ROW_MAJOR : (R, K/blk) row-major.
+ *            AVE_FP4_SF_TILED     : 128x4 tiles of 512 bytes, tile (rb, cb) at
+ *                                   (rb * ceil(K/blk/4) + cb) * 512, scale (r, c) inside a tile at
+ *                                   (r % 32) * 16 + (r / 32) * 4 + c; rows padded to 128 and scale
+ *                                   columns to 4 with zero bytes.  The GEMM consumes this layout.
+ *   global : one fp32 in device memory (NVFP4 only): value = nibble * scale * global.
+ */
+#ifndef AVE_FP4_H_
+#define AVE_FP4_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AVE_FP4_FMT_NVFP4 0
+#define AVE_FP4_FMT_MXFP4 1
+
+#define AVE_FP4_SF_ROW_MAJOR 0
+#define AVE_FP4_SF_TILED 1
+
+/* Kernel variants for ave_fp4_gemm (0 lets the library choose by shape). */
+#define AVE_FP4_GEMM_AUTO 0
+#define AVE_FP4_GEMM_1CTA_N128 1 /* 128x128 tile, two accumulator buffers */
+#define AVE_FP4_GEMM_1CTA_N256 2 /* 128x256 tile */
+#define AVE_FP4_GEMM_2CTA_N256 3 /* CTA pair, 256x256 tile */
+#define AVE_FP4_GEMM_2CTA_N128 4 /* CTA pair, 256x128 tile, two accumulator buffers */
+#define AVE_FP4_GEMM_SKINNY 10   /* M <= 64: operands swapped, stream-K over all SMs */
+
+/* Error codes returned as negative values. */
+#define AVE_FP4_ERR_ARG 1
+#define AVE_FP4_ERR_NOT_INIT 2
+#define AVE_FP4_ERR_WORKSPACE 3
+#define AVE_FP4_ERR_DEVICE 4
+
+/*
+ * One-time set-up for `device` (idempotent, thread-safe): checks that the device is
+ * sm_100, resolves the driver's tensor-map encoder, opts the kernels into large
+ * dynamic shared memory and allocates the 4-byte device status word.
+ * Replaces the load_binary / launcher-build step of the reference
+ * (python/avelang/backends/nvidia/driver.c:51-113, driver.py:182-336).
+ */
+int ave_fp4_init(int device);
+
+/* Message for the last non-zero return value on this thread (never NULL). */
+const char* ave_fp4_last_error(void);
+
+/* Bytes of the scale array of a (rows, k) operand in the given format and layout. */
+int64_t ave_fp4_sf_bytes(int64_t rows, int64_t k, int fmt, int sf_layout);
+
+/*
+ * Bytes of zero-initialised scratch ave_fp4_gemm needs for this shape on `device`
+ * (0 for shapes served by the tiled kernels).  The scratch must be all zero before
+ * its first use; the kernel leaves it reusable for the next call on the same stream.
+ */
+int64_t ave_fp4_workspace_bytes(int64_t m, int64_t n, int64_t k, int fmt, int variant, int device);
+
+/*
+ * max |x| of a (rows, k) bf16 matrix with row stride ldx (elements) -> *amax_f32
+ * (device fp32; the call zeroes it first).  k % 8 == 0, rows 16-byte aligned.
+ */
+int ave_fp4_amax(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void* amax_f32, void* stream);
+
+/*
+ * Quantise a (rows, k) bf16 matrix (row stride ldx elements, k % 32 == 0).
+ *   NVFP4: if amax_f32 != NULL the tensor scale is amax / 2688 (1 if amax == 0) and is
+ *          written to *global_scale; if amax_f32 == NULL the value already in
+ *          *global_scale is used (static scale).
+ *   MXFP4: amax_f32 and global_scale are ignored (may be NULL).
+ * No counterpart in the reference (it has no quantise operator); semantics are those
+ * of the CPU oracle.
+ */
+int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, int fmt, const void* amax_f32,
+                     void* global_scale, void* packed, void* scales, int sf_layout, void* stream);
+
+/* Row-major (rows, cols) scale bytes -> tiled layout (for weights quantised elsewhere). */
+int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, void* sf_tiled, void* stream);
+
+/*
+ * D (m, n) bf16, row stride ldd elements  =  A (m, k) * B (n, k)^T, fp32 accumulation,
+ * result scaled by (*a_global_scale) * (*b_global_scale) (NULL = 1) and rounded to
+ * bf16 (nearest even).  Scales in AVE_FP4_SF_TILED layout.
+ * Requirements: k % 32 == 0, ldd % 8 == 0, all pointers 16-byte aligned.
+ * Stands in for the kernel launch of gemm_pipeline_transposed_b
+ * (python/avelang_kernels/amdgpu_gemm.py:488-494).
+ */
+int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                 const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                 int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * Synchronises `stream`, reads and clears the device status word of the current
+ * device.  Returns 0 if every kernel since the last check ran to completion, or the
+ * positive status code a kernel recorded when one of its bounded waits expired
+ * (101 producer, 102 MMA issuer, 103 epilogue).  Not capturable.
+ */
+int ave_fp4_check(void* stream);
+
+/* Number of SMs the library sees on the current device (after ave_fp4_init). */
+int ave_fp4_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AVE_FP4_H_ */
