@@ -19,7 +19,7 @@ _inited: set[int] = set()
 # every symbol include/ave_fp4.h declares
 EXPORTS = (
     "ave_fp4_init", "ave_fp4_last_error", "ave_fp4_sf_bytes", "ave_fp4_workspace_bytes", "ave_fp4_amax",
-    "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count",
+    "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count", "ave_fp4_set_trace",
 )
 
 
@@ -56,6 +56,8 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_check.argtypes = [vp]
         L.ave_fp4_sm_count.restype = i32
         L.ave_fp4_sm_count.argtypes = []
+        L.ave_fp4_set_trace.restype = i32
+        L.ave_fp4_set_trace.argtypes = [vp, i64]
         _lib = L
         return L
 

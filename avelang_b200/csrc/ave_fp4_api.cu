@@ -53,6 +53,8 @@ struct DeviceState {
     bool ready = false;
     int sm_count = 0;
     int* status = nullptr;
+    long long* trace = nullptr;  // optional profiling buffer set by ave_fp4_set_trace
+    int trace_cap = 0;
 };
 
 std::mutex g_mutex;
@@ -150,15 +152,12 @@ template <int CG, int BN, int VEC, int ST, int ACC>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
-    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
     if ((rc = encode_packed(&tm_a, a, m, k, 128, "A"))) return rc;
     if ((rc = encode_packed(&tm_b, b, n, k, Cfg::kBnCta, "B"))) return rc;
     if ((rc = encode_sf(&tm_sfa, sfa, m, k, VEC, Cfg::kSfK, "A scales"))) return rc;
     if ((rc = encode_sf(&tm_sfb, sfb, n, k, VEC, Cfg::kSfK, "B scales"))) return rc;
-    if ((rc = encode_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d, static_cast<uint64_t>(n), static_cast<uint64_t>(m),
-                        static_cast<uint64_t>(ldd) * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, "D")))
-        return rc;
 
     GemmParams p;
     p.m = static_cast<int>(m);
@@ -169,7 +168,11 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.sf_k_atoms = static_cast<int>((k / VEC + 3) / 4);
     p.a_gs = ags;
     p.b_gs = bgs;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = static_cast<int>(ldd);
     p.status = ds.status;
+    p.trace = ds.trace;
+    p.trace_cap = ds.trace_cap;
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
@@ -188,7 +191,7 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p));
+    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
     return 0;
 }
 
@@ -435,6 +438,21 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
             return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: unknown variant %d", variant);
     }
 #undef GEMM_ARGS
+}
+
+int ave_fp4_set_trace(void* buffer, int64_t bytes) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (buffer == nullptr || bytes < 3 * 4 * 8) {
+        ds->trace = nullptr;
+        ds->trace_cap = 0;
+        return 0;
+    }
+    if (reinterpret_cast<uintptr_t>(buffer) & 7u) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_set_trace: buffer must be 8-byte aligned");
+    ds->trace = static_cast<long long*>(buffer);
+    ds->trace_cap = static_cast<int>(bytes / (3 * 4 * 8));
+    return 0;
 }
 
 int ave_fp4_check(void* stream) {

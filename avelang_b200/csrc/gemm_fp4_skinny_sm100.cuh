@@ -121,25 +121,54 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            // Loads are issued in bursts of kBurst consecutive K blocks: the weight tiles of a
+            // burst are neighbouring 128-byte pieces of the same 128 rows, so DRAM sees
+            // 512 contiguous bytes per row and page visit instead of 128.
+            constexpr int kBurst = 4;
+            static_assert(kBurst <= STAGES, "burst must fit in the ring");
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long u = u_begin; u < u_end && ok; ++u) {
-                const int tile = static_cast<int>(u / num_kb);
-                const int kb = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
-                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+            for (long long u = u_begin; u < u_end && ok;) {
+                const int g = (u_end - u < kBurst) ? static_cast<int>(u_end - u) : kBurst;
+                // slots are released in order, so a free last slot means the whole burst is free
+                const int last = stage + g - 1;
+                const int last_stage = last >= STAGES ? last - STAGES : last;
+                const uint32_t last_phase = last >= STAGES ? (phase ^ 1u) : phase;
+                if (!mbar_wait(bar_empty + last_stage * 8, last_phase ^ 1u)) {
                     atomicCAS(p.status, 0, kStatusTimeoutProducer);
                     ok = false;
                     break;
                 }
-                const uint32_t full = bar_full + stage * 8;
-                mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-                tma_load_2d<1>(smem_base + Cfg::kOffW + stage * Cfg::kWBytes, &tm_w, full, kb * 128, tile * 128);
-                tma_load_2d<1>(smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes, &tm_sfw, full, 0,
-                               tile * p.w_sf_k_atoms + kb * Cfg::kSfK);
-                tma_load_2d<1>(smem_base + Cfg::kOffX + stage * Cfg::kXBytes, &tm_x, full, kb * 128, 0);
-                tma_load_2d<1>(smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes, &tm_sfx, full, 0, kb * Cfg::kSfK);
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                int st[kBurst];
+                int tiles[kBurst];
+                int kbs[kBurst];
+#pragma unroll
+                for (int i = 0; i < kBurst; ++i) {
+                    if (i < g) {
+                        st[i] = stage;
+                        tiles[i] = static_cast<int>((u + i) / num_kb);
+                        kbs[i] = static_cast<int>((u + i) - static_cast<long long>(tiles[i]) * num_kb);
+                        mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kStageBytes);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kBurst; ++i)
+                    if (i < g)
+                        tma_load_2d<1>(smem_base + Cfg::kOffW + st[i] * Cfg::kWBytes, &tm_w, bar_full + st[i] * 8,
+                                       kbs[i] * 128, tiles[i] * 128);
+#pragma unroll
+                for (int i = 0; i < kBurst; ++i) {
+                    if (i < g) {
+                        const uint32_t full = bar_full + st[i] * 8;
+                        tma_load_2d<1>(smem_base + Cfg::kOffSfw + st[i] * Cfg::kSfBytes, &tm_sfw, full, 0,
+                                       tiles[i] * p.w_sf_k_atoms + kbs[i] * Cfg::kSfK);
+                        tma_load_2d<1>(smem_base + Cfg::kOffX + st[i] * Cfg::kXBytes, &tm_x, full, kbs[i] * 128, 0);
+                        tma_load_2d<1>(smem_base + Cfg::kOffSfx + st[i] * Cfg::kSfBytes, &tm_sfx, full, 0, kbs[i] * Cfg::kSfK);
+                    }
+                }
+                u += g;
             }
             if (ok) {
                 for (int i = 0; i < STAGES; ++i) {

@@ -9,9 +9,11 @@
 //     row chunk) and 128x4 scale-factor tiles into a STAGES-deep shared-memory ring;
 //   * warp 1: one thread issues tcgen05.cp (scale factors smem -> TMEM) and
 //     tcgen05.mma kind::mxf4nvf4 / kind::mxf4 block-scaled, fp32 accumulators in TMEM;
-//   * warps 2-5: epilogue -- tcgen05.ld, * alpha, round-to-nearest-even bf16,
-//     swizzled shared-memory staging, TMA store (coalesced 128-byte rows, clipped at
-//     the matrix edges).
+//   * warps 2-9: epilogue -- each warp drains 32 TMEM lanes x BLOCK_N/2 columns into
+//     registers (tcgen05.ld, * alpha, round-to-nearest-even bf16) and hands the
+//     accumulator back at once, so the next tile's MMAs start while the bf16 rows
+//     are still being written out through a swizzled shared-memory transpose as
+//     full 128-byte lines (predicated at the matrix edges).
 //
 // Operand convention (python/avelang_kernels/amdgpu_gemm.py:458-494): A is (M,K),
 // B is (N,K), both K-contiguous; D = A * B^T.
@@ -36,7 +38,11 @@ struct GemmParams {
     int sf_k_atoms;            // 128x4 scale tiles along K: ceil(K / SF_VEC / 4)
     const float* a_gs;         // device fp32 scalars (NVFP4 tensor scales) or nullptr
     const float* b_gs;
+    __nv_bfloat16* d;          // output, row stride ldd elements
+    int ldd;
     int* status;               // device status word, written on a wait timeout
+    long long* trace;          // optional clock64() stamps of CTA 0 (profiling aid), or nullptr
+    int trace_cap;             // records per role; record r of role q at trace[(q * trace_cap + r) * 4 ..+3]
 };
 
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
@@ -52,9 +58,10 @@ struct GemmConfig {
     static constexpr int kSfbBytes = kNb * kSfK * 512;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     static constexpr uint32_t kTxBytes = static_cast<uint32_t>(kStageBytes) * CTA_GROUP;
-    static constexpr int kEpiBufs = 2;
-    static constexpr int kEpiBufBytes = 32 * 128;       // 32 rows x 64 bf16
-    static constexpr int kEpiBytes = 4 * kEpiBufs * kEpiBufBytes;
+    static constexpr int kEpiWarps = 8;                 // two warps per TMEM lane quadrant
+    static constexpr int kEpiCols = BLOCK_N / 2;        // accumulator columns drained by one warp
+    static constexpr int kEpiBufBytes = 32 * 128;       // 32 rows x 64 bf16, one per epilogue warp
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufBytes;
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + STAGES * kABytes;
     static constexpr int kOffSfa = kOffB + STAGES * kBBytes;
@@ -69,7 +76,7 @@ struct GemmConfig {
     static constexpr int kTmemSfb = kTmemSfa + kSfK * 4;
     static constexpr int kTmemUsed = kTmemSfb + kSfK * kNb * 4;
     static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : kTmemUsed <= 256 ? 256 : 512;
-    static constexpr int kThreads = 192;
+    static constexpr int kThreads = 64 + 32 * kEpiWarps;
     static_assert(BLOCK_N % 128 == 0 && BLOCK_N <= 256, "BLOCK_N must be 128 or 256");
     static_assert(kTmemUsed <= 512, "tensor memory budget");
     static_assert(kOffB % 1024 == 0 && kOffSfa % 1024 == 0 && kOffEpi % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -90,10 +97,10 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
 }
 
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-                const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
+                const GemmParams p) {
     using Cfg = GemmConfig<CTA_GROUP, BLOCK_N, SF_VEC, STAGES, ACC_STAGES>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -120,14 +127,13 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         prefetch_tensormap(&tm_b);
         prefetch_tensormap(&tm_sfa);
         prefetch_tensormap(&tm_sfb);
-        prefetch_tensormap(&tm_d);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 1);
         }
         for (int a = 0; a < ACC_STAGES; ++a) {
             mbar_init(bar_tfull + a * 8, 1);
-            mbar_init(bar_tempty + a * 8, 4 * CTA_GROUP);
+            mbar_init(bar_tempty + a * 8, Cfg::kEpiWarps * CTA_GROUP);
         }
         fence_mbar_init();
     }
@@ -148,6 +154,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0);
+            int rec = 0;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 int tm, tn;
                 decode_tile(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -155,11 +163,13 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const int row_b = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBnCta;
                 const int sfa_atom0 = (row_a / 128) * p.sf_k_atoms;
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    const long long t0 = tr ? clock64() : 0;
                     if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
                         atomicCAS(p.status, 0, kStatusTimeoutProducer);
                         ok = false;
                         break;
                     }
+                    const long long t1 = tr ? clock64() : 0;
                     const uint32_t full = full0 + stage * 8;
                     if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
                     tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
@@ -171,6 +181,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
                                                &tm_sfb, full, 0,
                                                (tn * Cfg::kNb + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                    }
+                    if (tr && rec < p.trace_cap) {
+                        long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
+                        r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = stage;
+                        ++rec;
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -196,9 +211,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             uint32_t phase = 0;
             int tile_iter = 0;
             bool ok = true;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0);
+            int rec = 0;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_iter) {
                 const int acc = tile_iter % ACC_STAGES;
                 const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
+                const long long ta = tr ? clock64() : 0;
                 if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
                     atomicCAS(p.status, 0, kStatusTimeoutMma);
                     ok = false;
@@ -207,11 +225,13 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + Cfg::kTmemAcc + acc * BLOCK_N;
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    const long long t0 = tr ? (kb == 0 ? ta : clock64()) : 0;
                     if (!mbar_wait(bar_full + stage * 8, phase)) {
                         atomicCAS(p.status, 0, kStatusTimeoutMma);
                         ok = false;
                         break;
                     }
+                    const long long t1 = tr ? clock64() : 0;
                     tcgen05_fence_after();
                     const uint32_t sfa_s = smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes;
                     const uint32_t sfb_s = smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes;
@@ -237,6 +257,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             (kb > 0 || j > 0) ? 1u : 0u);
                     }
                     tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
+                    if (tr && rec < p.trace_cap) {
+                        long long* r = p.trace + (1ll * p.trace_cap + rec) * 4;
+                        r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = kb;
+                        ++rec;
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tcgen05_commit<CTA_GROUP>(bar_tfull + acc * 8);
@@ -244,41 +269,43 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
     } else {
         // --------------------------------------------------------------- epilogue
-        const int quad = warp & 3;  // TMEM lane quadrant this warp may access
-        const uint32_t stage_buf = smem_base + Cfg::kOffEpi + (warp - 2) * Cfg::kEpiBufs * Cfg::kEpiBufBytes;
+        const int quad = warp & 3;             // TMEM lane quadrant this warp may access
+        const int half = (warp - 2) >> 2;      // which half of the accumulator columns
+        const uint32_t sbuf = smem_base + Cfg::kOffEpi + (warp - 2) * Cfg::kEpiBufBytes;
         float alpha = 1.0f;
         if (p.a_gs) alpha *= __ldg(p.a_gs);
         if (p.b_gs) alpha *= __ldg(p.b_gs);
         const uint32_t tempty0 = (CTA_GROUP == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
+        constexpr int kChunks = Cfg::kEpiCols / 32;   // tcgen05.ld steps of 32 columns
+        constexpr int kGroups = Cfg::kEpiCols / 64;   // 128-byte output line groups
         int tile_iter = 0;
-        int buf = 0;
-        bool ok = true;
-        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_iter) {
+        for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
             int tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, tm, tn);
             const int acc = tile_iter % ACC_STAGES;
             const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0) && (warp == 2) && (lane == 0) && (tile_iter < p.trace_cap);
+            const long long te0 = tr ? clock64() : 0;
             if (!mbar_wait(bar_tfull + acc * 8, acc_phase)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
-                ok = false;
                 break;
             }
+            const long long te1 = tr ? clock64() : 0;
             tcgen05_fence_after();
             const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM + quad * 32;
-            const int col0 = tn * BLOCK_N;
-            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N;
-            constexpr int kChunks = BLOCK_N / 64;
-            uint32_t v[2][64];
-            tmem_ld_32x32b_x32(t_acc, reinterpret_cast<uint32_t(&)[32]>(v[0][0]));
-            tmem_ld_32x32b_x32(t_acc + 32, reinterpret_cast<uint32_t(&)[32]>(v[0][32]));
+            const int col0 = tn * BLOCK_N + half * Cfg::kEpiCols;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N +
+                                   half * Cfg::kEpiCols;
+            // ---- drain: TMEM -> registers (bf16 pairs), then give the accumulator back
+            uint32_t packed[kChunks * 16];
+            uint32_t v[2][32];
+            tmem_ld_32x32b_x32(t_acc, v[0]);
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
                 tmem_ld_wait();
                 if (c + 1 < kChunks) {
-                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 64, reinterpret_cast<uint32_t(&)[32]>(v[(c + 1) & 1][0]));
-                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[(c + 1) & 1][32]));
+                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 32, v[(c + 1) & 1]);
                 } else {
-                    // all accumulator columns of this tile are in registers: hand TMEM back
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) {
@@ -286,37 +313,50 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         else mbar_arrive(bar_tempty + acc * 8);
                     }
                 }
-                uint32_t packed[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const float lo = __uint_as_float(v[c & 1][2 * i]) * alpha;
                     const float hi = __uint_as_float(v[c & 1][2 * i + 1]) * alpha;
                     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                    packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                    packed[c * 16 + i] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                // staging buffer `buf` may still be read by the TMA store issued two chunks ago
-                if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+            }
+            const long long te2 = tr ? clock64() : 0;
+            // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so
+            // that every global store instruction writes four complete 128-byte lines
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
                 __syncwarp();
-                const uint32_t sbuf = stage_buf + buf * Cfg::kEpiBufBytes;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                    // 128-byte swizzle: 16-byte chunk q of row `lane` lives at chunk q ^ (lane & 7)
+                    // lane = row; 16-byte chunk q of the row lives at chunk q ^ (row & 7)
                     const uint32_t addr = sbuf + lane * 128 + ((q ^ (lane & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]),
-                                 "r"(packed[4 * q + 1]), "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[g * 32 + 4 * q]),
+                                 "r"(packed[g * 32 + 4 * q + 1]), "r"(packed[g * 32 + 4 * q + 2]),
+                                 "r"(packed[g * 32 + 4 * q + 3])
                                  : "memory");
                 }
-                fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    tma_store_2d(&tm_d, sbuf, col0 + c * 64, row0);
-                    tma_store_commit();
+                const int q = lane & 7;
+                const int col = col0 + g * 64 + q * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = i * 4 + (lane >> 3);
+                    const uint32_t addr = sbuf + r * 128 + ((q ^ (r & 7)) << 4);
+                    uint32_t w0, w1, w2, w3;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr) : "memory");
+                    const int row = row0 + r;
+                    if (row < p.m && col < p.n) {
+                        uint4* dst = reinterpret_cast<uint4*>(p.d + static_cast<size_t>(row) * p.ldd + col);
+                        *dst = make_uint4(w0, w1, w2, w3);
+                    }
                 }
-                buf ^= 1;
+            }
+            if (tr) {
+                long long* r = p.trace + (2ll * p.trace_cap + tile_iter) * 4;
+                r[0] = te0; r[1] = te1; r[2] = te2; r[3] = clock64();
             }
         }
-        if (lane == 0) tma_store_wait_all<0>();
-        __syncwarp();
     }
 
     tcgen05_fence_before();

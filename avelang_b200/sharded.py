@@ -1,0 +1,85 @@
+"""N-sharded FP4 linear layer: column-parallel GEMM plus an all-gather of the bf16 output.
+
+The reference has no multi-GPU code (single process, current device, current stream:
+python/avelang/backends/driver.py:24-32).  This module adds the one exchange step the
+sharded workload needs on a single NVLink/NVSwitch box: with B (N, K) split by rows
+across `world` ranks, rank r computes ``D[:, r*N/w:(r+1)*N/w] = A @ B_r.T`` with no
+inter-rank dependency, and the slices are exchanged with one all-gather.
+
+Layout of the gathered result: ``(world, M, N/world)`` -- rank r's column block is the
+contiguous slab ``gathered[r]``; ``columns_view`` presents it as the logical (M, N).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .fp4_gemm import Fp4Operand, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b, NVFP4
+
+
+def shard_bounds(n: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
+    """Rows [lo, hi) of the (N, K) weight owned by `rank`; every shard is a multiple of `align`."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}.")
+    if n % (world * align) != 0:
+        raise ValueError(f"N must be a multiple of world*{align} = {world * align}, got {n}.")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(weight_bf16: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """The slice of a full (N, K) bf16 weight this rank quantises and keeps."""
+    lo, hi = shard_bounds(weight_bf16.shape[0], world, rank)
+    return weight_bf16[lo:hi]
+
+
+def all_gather_columns(local: torch.Tensor, gathered: torch.Tensor | None = None, group=None) -> torch.Tensor:
+    """All-gather equal (M, n_local) slices into a (world, M, n_local) tensor (works on any backend)."""
+    world = dist.get_world_size(group)
+    if gathered is None:
+        gathered = torch.empty((world, *local.shape), dtype=local.dtype, device=local.device)
+    elif tuple(gathered.shape) != (world, *local.shape):
+        raise ValueError(f"gathered must have shape {(world, *local.shape)}, got {tuple(gathered.shape)}.")
+    dist.all_gather_into_tensor(gathered.view(-1, local.shape[-1]), local.contiguous(), group=group)
+    return gathered
+
+
+def columns_view(gathered: torch.Tensor) -> torch.Tensor:
+    """(world, M, n_local) -> logical (M, world * n_local) as a strided view (no copy)."""
+    world, m, n_local = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, world, n_local)
+
+
+class ShardedFp4Linear:
+    """Column-parallel ``y = x @ W.T`` with W sharded by rows (output columns).
+
+    The NVFP4 tensor scale of W must be computed over the whole tensor before sharding
+    (pass it to ``quantize_nvfp4(shard, global_scale=...)``), so that every rank's
+    shard dequantises exactly as the unsharded weight would.
+    """
+
+    def __init__(self, weight_shard: Fp4Operand, group=None):
+        self.weight = weight_shard
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._gathered: torch.Tensor | None = None
+
+    def local_forward(self, x: Fp4Operand, out: torch.Tensor | None = None) -> torch.Tensor:
+        fn = gemm_nvfp4_transposed_b if self.weight.fmt == NVFP4 else gemm_mxfp4_transposed_b
+        return fn(x, self.weight, out=out)
+
+    def forward(self, x: Fp4Operand) -> torch.Tensor:
+        """Returns the gathered (world, M, N/world) bf16 result (the buffer is reused between calls).
+
+        The local GEMM writes straight into this rank's slab of the gathered buffer and the
+        all-gather runs in place, so there is no staging copy.
+        """
+        m, n_local = x.rows, self.weight.rows
+        if self._gathered is None or tuple(self._gathered.shape) != (self.world, m, n_local):
+            self._gathered = torch.empty((self.world, m, n_local), dtype=torch.bfloat16, device=x.device)
+        local = self._gathered[self.rank]
+        self.local_forward(x, out=local)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self._gathered.view(-1, n_local), local, group=self.group)
+        return self._gathered

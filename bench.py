@@ -1,0 +1,433 @@
+#!/usr/bin/env python3
+"""Benchmark of the FP4 hot path.
+
+    python bench.py --gpus N --steps K --warmup W            (this repo's CUDA path)
+    python bench.py --impl reference --gpus N --steps K ...  (the oracle's CPU path on the host cores)
+
+One step = one pass of the hot path over one batch of synthetic input:
+
+  N = 1   the square NVFP4 GEMM  D = A * B^T  at M = N = K = 8192 (bf16 out) on operands
+          already quantised and resident in HBM.  Three operand sets are rotated so that the
+          working set (3 x 72 MB operands + 128 MB output) exceeds the 126 MB L2.
+  N > 1   the same per-GPU GEMM as one N-shard of an (8192, 8192*N, 8192) problem (weak scaling:
+          per-GPU work fixed), followed by the all-gather of the bf16 output over NVLink
+          -- the one exchange step the sharded path has.
+
+`value` is whole-job TFLOP/s (2*M*N*K per GPU per step, all ranks, divided by the slowest
+rank's device time).  `e2e` is the same metric through the public operators with HOST
+buffers: each step copies the bf16 activations A from pinned host memory, quantises them on
+the device, multiplies with the resident pre-quantised weights B and copies D back.
+
+The driver of the reference benchmark (benchmark/gemm/bench_amdgpu_gemm.py:23-68: warm-up,
+event timing, 2*M*N*K flops) is mirrored by benchmark/gemm/bench_fp4_gemm.py; this file is
+the machine-readable contract around the same measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "NVFP4 GEMM TFLOPS & % FP4 peak at 8192^3; decode-GEMM HBM GB/s"
+M = N = K = 8192
+NOMINAL_FP4_TFLOPS = 9000.0      # NVIDIA B200 datasheet, dense FP4
+NOMINAL_HBM_GBS = 8000.0         # figure the decode target is quoted against
+FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0
+NVLINK_GBS_PER_DIR = 770.0       # measured peer copy per direction on this pool
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+# (None until a capture of that kernel has been taken)
+NCU_TRAFFIC_BYTES = {"gemm_8192": None, "decode": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16=float(p["bf16_tflops"]), bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    except Exception:
+        return dict(bf16=FALLBACK_BF16_TFLOPS, bf16_sustained=1400.0, hbm=FALLBACK_HBM_GBS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        rows = []
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                try:
+                    rows.append((float(parts[0]), float(parts[1]), float(parts[2]), parts[3:7]))
+                except ValueError:
+                    pass
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        pmax = max(r[2] for r in rows)
+        busy = [r for r in rows if r[2] >= 0.5 * pmax] or rows
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in busy for i in range(4) if r[3][i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(r[0] for r in busy), "sm_max_mhz": rows[0][1], "power_w_max": pmax,
+                "samples": len(busy), "reasons": reasons}
+
+
+def dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local
+
+
+# ------------------------------------------------------------------------------------ ours
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    import avelang_b200 as ave
+    from avelang_b200 import sharded
+
+    world, rank, local = dist_env()
+    if world != args.gpus and world != 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the FP4 path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks = measured_peaks()
+    R = 3  # operand sets rotated so that consecutive steps do not hit L2-resident operands
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    A_ops, B_ops = [], []
+    host_a = None
+    for i in range(R):
+        a = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        b = torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        A_ops.append(ave.quantize_nvfp4(a))
+        B_ops.append(ave.quantize_nvfp4(b))
+        if i == 0:
+            host_a = [a.cpu().pin_memory()]
+        elif i < 2:
+            host_a.append(a.cpu().pin_memory())
+        del a, b
+    torch.cuda.synchronize(dev)
+
+    layers = [sharded.ShardedFp4Linear(B_ops[i]) for i in range(R)] if world > 1 else None
+    outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+
+    def step(i: int):
+        if world > 1:
+            layers[i % R].forward(A_ops[i % R])
+        else:
+            ave.gemm_nvfp4_transposed_b(A_ops[i % R], B_ops[i % R], out=outs[i % 2])
+
+    def timed(fn, steps: int, warmup: int) -> float:
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    total_ms = timed(step, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop() if sampler else None
+    ave.check_device_status(dev)
+    ms_per_step = total_ms / args.steps
+    flops_per_gpu = 2.0 * M * N * K
+    value = world * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+
+    # GEMM kernel alone (for the roofline object; at N = 1 this is the timed step itself)
+    if world > 1:
+        gemm_ms = timed(lambda i: ave.gemm_nvfp4_transposed_b(A_ops[i % R], B_ops[i % R], out=outs[i % 2]), args.steps,
+                        3) / args.steps
+        gath = layers[0]._gathered
+
+        def ag(i):
+            dist.all_gather_into_tensor(gath.view(-1, N), gath[rank])
+        ag_ms = timed(ag, max(5, args.steps // 2), 3) / max(5, args.steps // 2)
+    else:
+        gemm_ms, ag_ms = ms_per_step, None
+    gemm_tflops = flops_per_gpu / (gemm_ms * 1e-3) / 1e12
+    fp4_peak = 4.0 * peaks["bf16"]
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_fp4_kernel<2-CTA, 256x256x256>", "achieved": round(gemm_tflops, 1),
+        "peak": round(fp4_peak, 1), "unit": "TFLOP/s", "frac": round(gemm_tflops / fp4_peak, 4),
+        "peak_source": f"4 x cuBLAS bf16 burst ({peaks['bf16']:.0f} TF, {peaks['source']}): FP4 issues at 4x the bf16 rate",
+        "frac_of_nominal_9000": round(gemm_tflops / NOMINAL_FP4_TFLOPS, 4),
+        "frac_of_4x_sustained_bf16": round(gemm_tflops / (4.0 * peaks["bf16_sustained"]), 4),
+        "algorithmic_bytes": M * K // 2 + N * K // 2 + (M + N) * K // 16 + 2 * M * N,
+        "traffic": NCU_TRAFFIC_BYTES["gemm_8192"],
+    }
+    if world > 1:
+        nvlink_bytes = 2.0 * M * N * (world - 1)          # bytes each GPU must send (and receive)
+        t_flop = flops_per_gpu / (fp4_peak * 1e12)
+        t_link = nvlink_bytes / (NVLINK_GBS_PER_DIR * 1e9)
+        roofline["fused_step"] = {
+            "target_ms": round(max(t_flop, t_link) * 1e3, 4), "achieved_ms": round(ms_per_step, 4),
+            "frac": round(max(t_flop, t_link) * 1e3 / ms_per_step, 4), "bound": "nvlink" if t_link > t_flop else "tensor",
+            "gemm_only_ms": round(gemm_ms, 4), "allgather_only_ms": round(ag_ms, 4),
+            "gemm_only_tflops_per_gpu": round(gemm_tflops, 1),
+            "allgather_busbw_gbs": round(nvlink_bytes / (ag_ms * 1e-3) / 1e9, 1),
+        }
+
+    # ---- end to end through the public operators with host buffers
+    host_d = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    d_dev = outs[0]
+
+    def e2e_step(i: int):
+        a_dev.copy_(host_a[i % len(host_a)], non_blocking=True)
+        q = ave.quantize_nvfp4(a_dev)
+        if world > 1:
+            g = layers[i % R].forward(q)
+            host_d.copy_(g[rank], non_blocking=True)
+        else:
+            ave.gemm_nvfp4_transposed_b(q, B_ops[i % R], out=d_dev)
+            host_d.copy_(d_dev, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = timed(e2e_step, e2e_steps, 3) / e2e_steps
+    e2e = {"value": round(world * flops_per_gpu / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+           "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N, "ms_per_step": round(e2e_ms, 4),
+           "what": "pinned host bf16 A -> device, amax + NVFP4 quantise, GEMM with resident pre-quantised B, bf16 D -> pinned host"}
+
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale, fp32 accumulate, bf16 out)", "data": "synthetic",
+        "config": {"workload": "c1_square_nvfp4_8192" if world == 1 else f"c1_per_gpu_slice_of_8192x{8192 * world}x8192_plus_allgather",
+                   "m": M, "n_per_gpu": N, "k": K, "world": world,
+                   "l2": f"{R} operand sets rotated; working set {R}x72 MB + 2x128 MB output > 126 MB L2",
+                   "parallelism": f"n-sharded x{world} + bf16 all-gather" if world > 1 else "single gpu"},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+        "pct_of_nominal_fp4_peak": round(100.0 * value / world / NOMINAL_FP4_TFLOPS, 2),
+    }
+
+    if world == 1 and rank == 0:
+        if not args.skip_decode:
+            try:
+                out["decode"] = decode_bench(ave, torch, dev, peaks)
+            except Exception as exc:  # keep the headline line even if the side measurement fails
+                out["decode"] = {"error": repr(exc)}
+        if not args.skip_cpu_baseline:
+            try:
+                out["cpu_baseline"] = cpu_baseline(sample_rows=args.cpu_rows, repeats=1)
+            except Exception as exc:
+                out["cpu_baseline"] = {"error": repr(exc)}
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def decode_bench(ave, torch, dev, peaks) -> dict:
+    """Decode shape M=16, N=28672, K=8192: weights pre-quantised, activations (0.1 % outlier channels)
+    quantised on the fly.  Three weight sets are rotated (3 x 132 MB > L2).  Reports the GEMM kernel's
+    HBM GB/s on its 133 111 808 algorithmic bytes and the quantise+GEMM chain next to it."""
+    from avelang_b200 import inputs
+
+    m, n, k = 16, 28672, 8192
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    Ws = []
+    for _ in range(3):
+        w = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        Ws.append(ave.quantize_nvfp4(w))
+        del w
+    x = inputs.outlier_activations_bf16(m, k, seed=0).to(dev)
+    X = ave.quantize_nvfp4(x)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    algo_bytes = m * k // 2 + n * k // 2 + (m + n) * k // 16 + 2 * m * n
+
+    def timed(fn, steps):
+        for i in range(5):
+            fn(i)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / steps
+
+    # plain launches are host-bound at this size, so replay a captured graph of 3 GEMMs (one per weight set)
+    def three():
+        for W in Ws:
+            ave.gemm_nvfp4_transposed_b(X, W, out=out)
+
+    def chain():
+        for W in Ws:
+            q = ave.quantize_nvfp4(x)
+            ave.gemm_nvfp4_transposed_b(q, W, out=out)
+
+    res = {}
+    for name, fn in (("gemm", three), ("chain", chain)):
+        fn()
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream(dev)
+        with torch.cuda.graph(g, stream=s):
+            fn()
+        torch.cuda.synchronize(dev)
+        ms = min(timed(lambda i: g.replay(), 30) for _ in range(3)) / 3.0
+        res[name] = ms
+    ave.check_device_status(dev)
+    gbs = algo_bytes / (res["gemm"] * 1e-3) / 1e9
+    return {"workload": "c2_decode_16x28672x8192_nvfp4", "gemm_us": round(res["gemm"] * 1e3, 2), "gbs": round(gbs, 1),
+            "algorithmic_bytes": algo_bytes, "frac_of_measured_hbm": round(gbs / peaks["hbm"], 4),
+            "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4),
+            "quantise_plus_gemm_us": round(res["chain"] * 1e3, 2), "timing": "CUDA graph of 3 launches (3 weight sets), replayed",
+            "traffic": NCU_TRAFFIC_BYTES["decode"]}
+
+
+# ----------------------------------------------------------------------------- CPU oracle
+def cpu_oracle_step(O, np, torch, a_bits, qb, n_rows):
+    """The oracle path on the host: quantise the activation rows, dequantise both operands,
+    fp32 matmul (the reference's expression on CPU tensors), round to bf16."""
+    qa = O.c_quantize(a_bits[:n_rows], O.NVFP4)
+    a_hat = O.c_dequantize(*qa, O.NVFP4)
+    b_hat = O.c_dequantize(*qb, O.NVFP4)
+    d32 = torch.from_numpy(a_hat) @ torch.from_numpy(b_hat).T
+    return d32.to(torch.bfloat16)
+
+
+def cpu_baseline(sample_rows: int, repeats: int = 1) -> dict:
+    import numpy as np
+    import torch
+
+    from oracle import fp4_oracle as O
+
+    O.build()
+    rng = np.random.default_rng(0)
+    a_bits = O.f32_to_bf16_bits(rng.standard_normal((sample_rows, K), dtype=np.float32))
+    b_bits = O.f32_to_bf16_bits(rng.standard_normal((N, K), dtype=np.float32))
+    qb = O.c_quantize(b_bits, O.NVFP4)          # weights are pre-quantised, as on the GPU arm
+    cpu_oracle_step(O, np, torch, a_bits, qb, min(8, sample_rows))  # warm-up
+    ts = []
+    for _ in range(max(1, repeats)):
+        t0 = time.perf_counter()
+        cpu_oracle_step(O, np, torch, a_bits, qb, sample_rows)
+        ts.append(time.perf_counter() - t0)
+    t = statistics.median(ts)
+    flops = 2.0 * sample_rows * N * K
+    return {"value": round(flops / t / 1e12, 5), "unit": "TFLOP/s", "cores": int(torch.get_num_threads()), "kind": "port",
+            "sample": f"{sample_rows} of {M} rows of A against the full 8192x8192 B: quantise A rows, dequantise A and B, "
+                      f"fp32 matmul (torch CPU), bf16 round; {t:.2f} s per pass",
+            "seconds": round(t, 3), "omp_threads": O.num_threads()}
+
+
+def run_reference(args) -> dict:
+    """The reference arm: the oracle's CPU path on the host cores (the reference project has no FP4
+    implementation and cannot be built here, so the oracle port is the reference for this path)."""
+    world, rank, _ = dist_env()
+    if rank != 0:
+        return {}
+    import numpy as np
+    import torch
+
+    from oracle import fp4_oracle as O
+
+    O.build()
+    rows = args.cpu_rows
+    rng = np.random.default_rng(0)
+    a_bits = O.f32_to_bf16_bits(rng.standard_normal((rows, K), dtype=np.float32))
+    b_bits = O.f32_to_bf16_bits(rng.standard_normal((N, K), dtype=np.float32))
+    qb = O.c_quantize(b_bits, O.NVFP4)
+    # size the sample so that steps + warm-up stay within ~3 minutes
+    t0 = time.perf_counter()
+    cpu_oracle_step(O, np, torch, a_bits, qb, rows)
+    t_one = time.perf_counter() - t0
+    budget = 150.0
+    total = args.steps + args.warmup
+    while rows > 8 and t_one * total > budget:
+        rows //= 2
+        t0 = time.perf_counter()
+        cpu_oracle_step(O, np, torch, a_bits, qb, rows)
+        t_one = time.perf_counter() - t0
+    for _ in range(args.warmup):
+        cpu_oracle_step(O, np, torch, a_bits, qb, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_step(O, np, torch, a_bits, qb, rows)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 2.0 * rows * N * K / dt / 1e12
+    cores = int(torch.get_num_threads())
+    sample = (f"each step = {rows} of {M} rows of A against the full 8192x8192 B: quantise A rows, dequantise A and B, "
+              f"fp32 matmul (torch CPU), bf16 round")
+    return {
+        "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (dequantised E2M1 x scale)", "data": "synthetic",
+        "config": {"workload": "c1_square_nvfp4_8192", "m": M, "n_per_gpu": N, "k": K, "sample_rows": rows},
+        "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-rows", type=int, default=512, help="rows of A in the CPU baseline sample")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-decode", action="store_true")
+    args = ap.parse_args()
+    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if res:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -124,6 +124,16 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
  */
 int ave_fp4_check(void* stream);
 
+/*
+ * Profiling aid (no counterpart in the reference, whose only tracing is event timing in
+ * benchmark/gemm/bench_amdgpu_gemm.py:43-52).  While a device buffer is set, the tiled GEMM
+ * kernels make CTA 0 record clock64() stamps: with cap = bytes / 96, record r of role q
+ * (0 = TMA producer, 1 = MMA issuer, per K block; 2 = first epilogue warp, per tile) is four
+ * int64 at buffer[(q * cap + r) * 4]: {before wait, after wait, after issue / drain, aux}.
+ * Pass NULL to switch it off (the default).
+ */
+int ave_fp4_set_trace(void* buffer, int64_t bytes);
+
 /* Number of SMs the library sees on the current device (after ave_fp4_init). */
 int ave_fp4_sm_count(void);
 
