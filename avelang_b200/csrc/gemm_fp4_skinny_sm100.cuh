@@ -79,7 +79,8 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const int warp = threadIdx.x >> 5;
+    // warp-uniform values via a shuffle broadcast: keeps issue-loop state in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
     const long long units = static_cast<long long>(p.tiles_n) * num_kb;
@@ -116,11 +117,13 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_ptr_gen;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_gen, 0);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // the whole warp walks the loop (warp-uniform state); one elected lane issues
+        {
+            const bool issuer = elect_one_sync();
             // Loads are issued in bursts of kBurst consecutive K blocks: the weight tiles of a
             // burst are neighbouring 128-byte pieces of the same 128 rows, so DRAM sees
             // 512 contiguous bytes per row and page visit instead of 128.
@@ -136,7 +139,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 const int last_stage = last >= STAGES ? last - STAGES : last;
                 const uint32_t last_phase = last >= STAGES ? (phase ^ 1u) : phase;
                 if (!mbar_wait(bar_empty + last_stage * 8, last_phase ^ 1u)) {
-                    atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                    if (issuer) atomicCAS(p.status, 0, kStatusTimeoutProducer);
                     ok = false;
                     break;
                 }
@@ -149,18 +152,18 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                         st[i] = stage;
                         tiles[i] = static_cast<int>((u + i) / num_kb);
                         kbs[i] = static_cast<int>((u + i) - static_cast<long long>(tiles[i]) * num_kb);
-                        mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kStageBytes);
+                        if (issuer) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kStageBytes);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
                 }
 #pragma unroll
                 for (int i = 0; i < kBurst; ++i)
-                    if (i < g)
+                    if (i < g && issuer)
                         tma_load_2d<1>(smem_base + Cfg::kOffW + st[i] * Cfg::kWBytes, &tm_w, bar_full + st[i] * 8,
                                        kbs[i] * 128, tiles[i] * 128);
 #pragma unroll
                 for (int i = 0; i < kBurst; ++i) {
-                    if (i < g) {
+                    if (i < g && issuer) {
                         const uint32_t full = bar_full + st[i] * 8;
                         tma_load_2d<1>(smem_base + Cfg::kOffSfw + st[i] * Cfg::kSfBytes, &tm_sfw, full, 0,
                                        tiles[i] * p.w_sf_k_atoms + kbs[i] * Cfg::kSfK);
@@ -173,17 +176,19 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             if (ok) {
                 for (int i = 0; i < STAGES; ++i) {
                     if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
-                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        if (issuer) atomicCAS(p.status, 0, kStatusTimeoutProducer);
                         break;
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        {
             constexpr bool kUe8m0 = (SF_VEC == 32);
+            const bool issuer = elect_one_sync();
             int stage = 0;
             uint32_t phase = 0;
             int seg = 0;
@@ -195,7 +200,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 const int acc = seg % ACC;
                 const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
                 if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
-                    atomicCAS(p.status, 0, kStatusTimeoutMma);
+                    if (issuer) atomicCAS(p.status, 0, kStatusTimeoutMma);
                     ok = false;
                     break;
                 }
@@ -203,35 +208,40 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 const uint32_t d_tmem = tmem_base + acc * MP;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(bar_full + stage * 8, phase)) {
-                        atomicCAS(p.status, 0, kStatusTimeoutMma);
+                        if (issuer) atomicCAS(p.status, 0, kStatusTimeoutMma);
                         ok = false;
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t sfw_s = smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes;
-                    const uint32_t sfx_s = smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes;
-#pragma unroll
-                    for (int j = 0; j < Cfg::kSfK; ++j) {
-                        tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfw + j * 4, make_desc_sf(sfw_s + j * 512));
-                        tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfx + j * 4, make_desc_sf(sfx_s + j * 512));
-                    }
+                    const uint64_t sfw_desc = make_desc_sf(smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes);
+                    const uint64_t sfx_desc = make_desc_sf(smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes);
                     const uint64_t w_desc = make_desc_k_sw128(smem_base + Cfg::kOffW + stage * Cfg::kWBytes);
                     const uint64_t x_desc = make_desc_k_sw128(smem_base + Cfg::kOffX + stage * Cfg::kXBytes);
+                    const uint32_t accum0 = (kb > kb0) ? 1u : 0u;
+                    if (issuer) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int sf_tile = (SF_VEC == 16) ? j : (j >> 1);
-                        const int sf_id = (SF_VEC == 16) ? 0 : 2 * (j & 1);
-                        const uint32_t idesc = make_idesc_fp4(128, MP, kUe8m0, sf_id);
-                        mma_fp4_block_scaled<1, SF_VEC>(d_tmem, w_desc + static_cast<uint64_t>(j * 2),
-                                                        x_desc + static_cast<uint64_t>(j * 2), idesc,
-                                                        tmem_base + Cfg::kTmemSfw + sf_tile * 4,
-                                                        tmem_base + Cfg::kTmemSfx + sf_tile * 4,
-                                                        (kb > kb0 || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < Cfg::kSfK; ++j) {
+                            // descriptor start address is in 16-byte units: one 512-byte scale tile = 32
+                            tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfw + j * 4, sfw_desc + static_cast<uint64_t>(j * 32));
+                            tmem_cp_sf<1>(tmem_base + Cfg::kTmemSfx + j * 4, sfx_desc + static_cast<uint64_t>(j * 32));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            constexpr bool nv = (SF_VEC == 16);
+                            const int sf_tile = nv ? j : (j >> 1);
+                            const int sf_id = nv ? 0 : 2 * (j & 1);
+                            const uint32_t idesc = make_idesc_fp4(128, MP, kUe8m0, sf_id);
+                            mma_fp4_block_scaled<1, SF_VEC>(d_tmem, w_desc + static_cast<uint64_t>(j * 2),
+                                                            x_desc + static_cast<uint64_t>(j * 2), idesc,
+                                                            tmem_base + Cfg::kTmemSfw + sf_tile * 4,
+                                                            tmem_base + Cfg::kTmemSfx + sf_tile * 4, (j > 0) ? 1u : accum0);
+                        }
+                        tcgen05_commit<1>(bar_empty + stage * 8);
                     }
-                    tcgen05_commit<1>(bar_empty + stage * 8);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tcgen05_commit<1>(bar_tfull + acc * 8);
+                if (ok && issuer) tcgen05_commit<1>(bar_tfull + acc * 8);
+                __syncwarp();
                 u += kb1 - kb0;
             }
         }

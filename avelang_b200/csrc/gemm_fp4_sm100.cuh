@@ -106,9 +106,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const int warp = threadIdx.x >> 5;
+    // Warp-uniform values go through a shuffle broadcast so that the compiler keeps them, and
+    // the addresses and descriptors derived from them, in uniform registers: the TMA and tcgen05
+    // instructions read their operands from there, and the issue loops below stay cheap.
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const uint32_t cta_rank = (CTA_GROUP == 2) ? cluster_ctarank() : 0u;
+    const uint32_t cta_rank = (CTA_GROUP == 2) ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
     const bool is_leader = (cta_rank == 0);
     const int cluster_id = blockIdx.x / CTA_GROUP;
     const int num_clusters = gridDim.x / CTA_GROUP;
@@ -145,11 +148,13 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     __syncthreads();
     if constexpr (CTA_GROUP == 2) cluster_sync_all();
     tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_ptr_gen;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_gen, 0);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp walks the loop (so loop state is warp-uniform); one elected lane issues.
+        {
+            const bool issuer = elect_one_sync();
             const uint32_t full0 = (CTA_GROUP == 2) ? mapa_shared(bar_full, 0) : bar_full;
             int stage = 0;
             uint32_t phase = 0;
@@ -165,28 +170,30 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const long long t0 = tr ? clock64() : 0;
                     if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
-                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        if (issuer) atomicCAS(p.status, 0, kStatusTimeoutProducer);
                         ok = false;
                         break;
                     }
                     const long long t1 = tr ? clock64() : 0;
                     const uint32_t full = full0 + stage * 8;
-                    if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
-                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
-                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
-                    tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
-                                           sfa_atom0 + kb * Cfg::kSfK);
+                    if (issuer) {
+                        if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
+                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
+                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
+                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
+                                               sfa_atom0 + kb * Cfg::kSfK);
 #pragma unroll
-                    for (int nb = 0; nb < Cfg::kNb; ++nb) {
-                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
-                                               &tm_sfb, full, 0,
-                                               (tn * Cfg::kNb + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                        for (int nb = 0; nb < Cfg::kNb; ++nb) {
+                            tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
+                                                   &tm_sfb, full, 0,
+                                                   (tn * Cfg::kNb + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                        }
+                        if (tr && rec < p.trace_cap) {
+                            long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
+                            r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = stage;
+                        }
                     }
-                    if (tr && rec < p.trace_cap) {
-                        long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
-                        r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = stage;
-                        ++rec;
-                    }
+                    ++rec;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -195,18 +202,20 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 // copy is in flight and no peer signal is outstanding when the CTA exits.
                 for (int i = 0; i < STAGES; ++i) {
                     if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
-                        atomicCAS(p.status, 0, kStatusTimeoutProducer);
+                        if (issuer) atomicCAS(p.status, 0, kStatusTimeoutProducer);
                         break;
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
-        if (lane == 0 && is_leader) {
+        if (is_leader) {
             constexpr int kMmaM = 128 * CTA_GROUP;
             constexpr bool kUe8m0 = (SF_VEC == 32);
+            const bool issuer = elect_one_sync();
             int stage = 0;
             uint32_t phase = 0;
             int tile_iter = 0;
@@ -218,7 +227,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
                 const long long ta = tr ? clock64() : 0;
                 if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
-                    atomicCAS(p.status, 0, kStatusTimeoutMma);
+                    if (issuer) atomicCAS(p.status, 0, kStatusTimeoutMma);
                     ok = false;
                     break;
                 }
@@ -227,7 +236,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const long long t0 = tr ? (kb == 0 ? ta : clock64()) : 0;
                     if (!mbar_wait(bar_full + stage * 8, phase)) {
-                        atomicCAS(p.status, 0, kStatusTimeoutMma);
+                        if (issuer) atomicCAS(p.status, 0, kStatusTimeoutMma);
                         ok = false;
                         break;
                     }
@@ -235,36 +244,44 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     tcgen05_fence_after();
                     const uint32_t sfa_s = smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes;
                     const uint32_t sfb_s = smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes;
-#pragma unroll
-                    for (int j = 0; j < Cfg::kSfK; ++j) {
-                        tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfa + j * 4, make_desc_sf(sfa_s + j * 512));
-#pragma unroll
-                        for (int nb = 0; nb < Cfg::kNb; ++nb)
-                            tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfb + (j * Cfg::kNb + nb) * 4,
-                                                  make_desc_sf(sfb_s + (nb * Cfg::kSfK + j) * 512));
-                    }
+                    const uint64_t sfa_desc = make_desc_sf(sfa_s);
+                    const uint64_t sfb_desc = make_desc_sf(sfb_s);
                     const uint64_t a_desc = make_desc_k_sw128(smem_base + Cfg::kOffA + stage * Cfg::kABytes);
                     const uint64_t b_desc = make_desc_k_sw128(smem_base + Cfg::kOffB + stage * Cfg::kBBytes);
+                    const uint32_t accum0 = (kb > 0) ? 1u : 0u;
+                    if (issuer) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // one K=64 step = 32 bytes along the swizzled 128-byte row
-                        const int sf_tile = (SF_VEC == 16) ? j : (j >> 1);
-                        const int sf_id = (SF_VEC == 16) ? 0 : 2 * (j & 1);
-                        const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
-                        mma_fp4_block_scaled<CTA_GROUP, SF_VEC>(
-                            d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
-                            tmem_base + Cfg::kTmemSfa + sf_tile * 4, tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4,
-                            (kb > 0 || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < Cfg::kSfK; ++j) {
+                            // descriptor start address is in 16-byte units: one 512-byte scale tile = 32
+                            tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfa + j * 4, sfa_desc + static_cast<uint64_t>(j * 32));
+#pragma unroll
+                            for (int nb = 0; nb < Cfg::kNb; ++nb)
+                                tmem_cp_sf<CTA_GROUP>(tmem_base + Cfg::kTmemSfb + (j * Cfg::kNb + nb) * 4,
+                                                      sfb_desc + static_cast<uint64_t>((nb * Cfg::kSfK + j) * 32));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // one K=64 step = 32 bytes along the swizzled 128-byte row = 2 address units
+                            constexpr bool nv = (SF_VEC == 16);
+                            const int sf_tile = nv ? j : (j >> 1);
+                            const int sf_id = nv ? 0 : 2 * (j & 1);
+                            const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
+                            mma_fp4_block_scaled<CTA_GROUP, SF_VEC>(
+                                d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
+                                tmem_base + Cfg::kTmemSfa + sf_tile * 4, tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4,
+                                (j > 0) ? 1u : accum0);
+                        }
+                        tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
+                        if (tr && rec < p.trace_cap) {
+                            long long* r = p.trace + (1ll * p.trace_cap + rec) * 4;
+                            r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = kb;
+                        }
                     }
-                    tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
-                    if (tr && rec < p.trace_cap) {
-                        long long* r = p.trace + (1ll * p.trace_cap + rec) * 4;
-                        r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = kb;
-                        ++rec;
-                    }
+                    ++rec;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tcgen05_commit<CTA_GROUP>(bar_tfull + acc * 8);
+                if (ok && issuer) tcgen05_commit<CTA_GROUP>(bar_tfull + acc * 8);
+                __syncwarp();
             }
         }
     } else {
@@ -276,7 +293,6 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (p.a_gs) alpha *= __ldg(p.a_gs);
         if (p.b_gs) alpha *= __ldg(p.b_gs);
         const uint32_t tempty0 = (CTA_GROUP == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
-        constexpr int kChunks = Cfg::kEpiCols / 32;   // tcgen05.ld steps of 32 columns
         constexpr int kGroups = Cfg::kEpiCols / 64;   // 128-byte output line groups
         int tile_iter = 0;
         for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
@@ -296,30 +312,25 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const int col0 = tn * BLOCK_N + half * Cfg::kEpiCols;
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N +
                                    half * Cfg::kEpiCols;
-            // ---- drain: TMEM -> registers (bf16 pairs), then give the accumulator back
-            uint32_t packed[kChunks * 16];
-            uint32_t v[2][32];
-            tmem_ld_32x32b_x32(t_acc, v[0]);
+            // ---- drain: all of this warp's accumulator columns go to registers with the loads in
+            // flight together (one round trip), then the accumulator is handed back at once
+            uint32_t packed[Cfg::kEpiCols];
 #pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-                tmem_ld_wait();
-                if (c + 1 < kChunks) {
-                    tmem_ld_32x32b_x32(t_acc + (c + 1) * 32, v[(c + 1) & 1]);
-                } else {
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(tempty0 + acc * 8);
-                        else mbar_arrive(bar_tempty + acc * 8);
-                    }
-                }
+            for (int c = 0; c < Cfg::kEpiCols / 64; ++c) tmem_ld_32x32b_x64(t_acc + c * 64, &packed[c * 64]);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(tempty0 + acc * 8);
+                else mbar_arrive(bar_tempty + acc * 8);
+            }
+            // fp32 -> bf16 pairs in place: word i takes columns 2i and 2i+1
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float lo = __uint_as_float(v[c & 1][2 * i]) * alpha;
-                    const float hi = __uint_as_float(v[c & 1][2 * i + 1]) * alpha;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                    packed[c * 16 + i] = *reinterpret_cast<uint32_t*>(&h);
-                }
+            for (int i = 0; i < Cfg::kEpiCols / 2; ++i) {
+                const float lo = __uint_as_float(packed[2 * i]) * alpha;
+                const float hi = __uint_as_float(packed[2 * i + 1]) * alpha;
+                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                packed[i] = *reinterpret_cast<uint32_t*>(&h);
             }
             const long long te2 = tr ? clock64() : 0;
             // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so
