@@ -3,6 +3,7 @@ from .fp4_gemm import (  # noqa: F401
     GEMM_1CTA_N128,
     GEMM_1CTA_N256,
     GEMM_2CTA_N128,
+    GEMM_2CTA_N192,
     GEMM_2CTA_N256,
     GEMM_AUTO,
     GEMM_SKINNY,
@@ -15,6 +16,7 @@ from .fp4_gemm import (  # noqa: F401
     gemm_mxfp4_transposed_b,
     gemm_nvfp4_transposed_b,
     make_operand,
+    pack_weight_tiles,
     quantize_mxfp4,
     quantize_nvfp4,
     to_tiled,
@@ -22,6 +24,6 @@ from .fp4_gemm import (  # noqa: F401
 
 __all__ = [
     "Fp4Operand", "quantize_nvfp4", "quantize_mxfp4", "gemm_nvfp4_transposed_b", "gemm_mxfp4_transposed_b",
-    "make_operand", "to_tiled", "check_device_status", "NVFP4", "MXFP4", "SF_ROW_MAJOR", "SF_TILED",
-    "GEMM_AUTO", "GEMM_1CTA_N128", "GEMM_1CTA_N256", "GEMM_2CTA_N256", "GEMM_2CTA_N128", "GEMM_SKINNY",
+    "make_operand", "pack_weight_tiles", "to_tiled", "check_device_status", "NVFP4", "MXFP4", "SF_ROW_MAJOR", "SF_TILED",
+    "GEMM_AUTO", "GEMM_1CTA_N128", "GEMM_1CTA_N256", "GEMM_2CTA_N256", "GEMM_2CTA_N128", "GEMM_2CTA_N192", "GEMM_SKINNY",
 ]

@@ -78,7 +78,7 @@ cudaError_t prepare_skinny() {
 }
 
 // Stage counts per tile shape (shared-memory budget 227 KB per CTA).
-constexpr int kSt1N128 = 5, kSt1N256 = 3, kSt2N256 = 5, kSt2N128 = 6;
+constexpr int kSt1N128 = 5, kSt1N256 = 3, kSt2N256 = 5, kSt2N128 = 6, kSt2N192 = 5;
 constexpr int kStSkinny16 = 8, kStSkinny32 = 8, kStSkinny64 = 7;
 
 cudaError_t prepare_all() {
@@ -90,6 +90,8 @@ cudaError_t prepare_all() {
     PREP((prepare_gemm<1, 256, 32, kSt1N256, 1>()));
     PREP((prepare_gemm<2, 256, 16, kSt2N256, 1>()));
     PREP((prepare_gemm<2, 256, 32, kSt2N256, 1>()));
+    PREP((prepare_gemm<2, 192, 16, kSt2N192, 2>()));
+    PREP((prepare_gemm<2, 192, 32, kSt2N192, 2>()));
     PREP((prepare_gemm<2, 128, 16, kSt2N128, 2>()));
     PREP((prepare_gemm<2, 128, 32, kSt2N128, 2>()));
     PREP((prepare_skinny<16, 16, kStSkinny16>()));
@@ -209,11 +211,19 @@ int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
 template <int MP, int VEC, int ST>
 int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const float* xgs, const void* w, const void* sfw,
                   const float* wgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, void* workspace,
-                  cudaStream_t stream) {
+                  bool w_tile_major, cudaStream_t stream) {
     using Cfg = SkinnyConfig<MP, VEC, ST>;
     CUtensorMap tm_w, tm_x, tm_sfw, tm_sfx;
     int rc;
-    if ((rc = encode_packed(&tm_w, w, n, k, 128, "B"))) return rc;
+    if (w_tile_major) {
+        // tile-major weights: every 128-byte row piece of every 16 KB tile is one row of a (tiles*128, 128) matrix
+        const uint64_t tile_rows = static_cast<uint64_t>((n + 127) / 128) * static_cast<uint64_t>((k + 255) / 256) * 128;
+        if ((rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, 128, tile_rows, 128, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B,
+                            "B (tile-major)")))
+            return rc;
+    } else if ((rc = encode_packed(&tm_w, w, n, k, 128, "B"))) {
+        return rc;
+    }
     if ((rc = encode_packed(&tm_x, x, m, k, MP, "A"))) return rc;
     if ((rc = encode_sf(&tm_sfw, sfw, n, k, VEC, Cfg::kSfK, "B scales"))) return rc;
     if ((rc = encode_sf(&tm_sfx, sfx, m, k, VEC, Cfg::kSfK, "A scales"))) return rc;
@@ -225,12 +235,15 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.tiles_n = static_cast<int>((n + 127) / 128);
     p.w_sf_k_atoms = static_cast<int>((k / VEC + 3) / 4);
     p.ldd = static_cast<int>(ldd);
+    p.w_tile_major = w_tile_major ? 1 : 0;
     p.x_gs = xgs;
     p.w_gs = wgs;
     p.d = static_cast<__nv_bfloat16*>(d);
     p.counters = static_cast<int*>(workspace);
     p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + skinny_counter_bytes(n));
     p.status = ds.status;
+    p.trace = ds.trace;
+    p.trace_cap = ds.trace_cap;
 
     const long long units = static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
     long long grid = ds.sm_count;
@@ -242,6 +255,7 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
 }
 
 int resolve_variant(int variant, int64_t m, int64_t n) {
+    if (variant == AVE_FP4_GEMM_SKINNY_TILED_W) return AVE_FP4_GEMM_SKINNY;
     if (variant != AVE_FP4_GEMM_AUTO) return variant;
     if (m <= 64) return AVE_FP4_GEMM_SKINNY;
     (void)n;
@@ -390,6 +404,26 @@ int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, vo
     return 0;
 }
 
+int64_t ave_fp4_weight_tiles_bytes(int64_t n, int64_t k) { return ((n + 127) / 128) * ((k + 255) / 256) * 16384; }
+
+int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k, void* packed_tiles, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (n < 0 || k < 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_pack_weight_tiles: K must be a multiple of 32");
+    if (n == 0 || k == 0) return 0;
+    if (!packed_row_major || !packed_tiles || !aligned16(packed_row_major) || !aligned16(packed_tiles))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_pack_weight_tiles: null or misaligned pointer");
+    const long long total = ave_fp4_weight_tiles_bytes(n, k) / 16;
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(ds->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    pack_weight_tiles_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(packed_row_major), n, k / 2, static_cast<uint8_t*>(packed_tiles));
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
                  const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream) {
@@ -421,13 +455,15 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
             return nv ? launch_gemm<2, 256, 16, kSt2N256, 1>(GEMM_ARGS) : launch_gemm<2, 256, 32, kSt2N256, 1>(GEMM_ARGS);
         case AVE_FP4_GEMM_2CTA_N128:
             return nv ? launch_gemm<2, 128, 16, kSt2N128, 2>(GEMM_ARGS) : launch_gemm<2, 128, 32, kSt2N128, 2>(GEMM_ARGS);
+        case AVE_FP4_GEMM_2CTA_N192:
+            return nv ? launch_gemm<2, 192, 16, kSt2N192, 2>(GEMM_ARGS) : launch_gemm<2, 192, 32, kSt2N192, 2>(GEMM_ARGS);
         case AVE_FP4_GEMM_SKINNY: {
             if (m > 64) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: the skinny variant needs M <= 64, got %lld", static_cast<long long>(m));
             const int64_t need = skinny_workspace_bytes(m, n, ds->sm_count);
             if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
                 return fail(-AVE_FP4_ERR_WORKSPACE, "ave_fp4_gemm: workspace of %lld bytes (256-byte aligned, zero-initialised) required, got %lld",
                             static_cast<long long>(need), static_cast<long long>(workspace ? workspace_bytes : 0));
-#define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, s
+#define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, variant == AVE_FP4_GEMM_SKINNY_TILED_W, s
             const int mp = skinny_mp(m);
             if (mp == 16) return nv ? launch_skinny<16, 16, kStSkinny16>(SKINNY_ARGS) : launch_skinny<16, 32, kStSkinny16>(SKINNY_ARGS);
             if (mp == 32) return nv ? launch_skinny<32, 16, kStSkinny32>(SKINNY_ARGS) : launch_skinny<32, 32, kStSkinny32>(SKINNY_ARGS);

@@ -28,12 +28,15 @@ struct SkinnyParams {
     int tiles_n;          // ceil(N / 128)
     int w_sf_k_atoms;     // scale tiles along K
     int ldd;              // row stride of D in elements
+    int w_tile_major;     // 0: W packed row-major (N, K/2); 1: 16 KB tiles [N/128][K/256][128 rows][128 B]
     const float* x_gs;    // device fp32 tensor scales or nullptr
     const float* w_gs;
     __nv_bfloat16* d;
     float* partials;      // gridDim.x * 2 * MP * 128 fp32
     int* counters;        // 4 * tiles_n ints, zero on entry, zero again on exit
     int* status;
+    long long* trace;     // optional clock64() stamps of CTA 0 (same record layout as the tiled kernel)
+    int trace_cap;
 };
 
 template <int MP, int SF_VEC, int STAGES>
@@ -95,28 +98,37 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const uint32_t tmem_ptr_smem = smem_base + Cfg::kOffTmemPtr;
     volatile uint32_t* tmem_ptr_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kOffTmemPtr);
 
-    if (threadIdx.x == 0) {
-        prefetch_tensormap(&tm_w);
-        prefetch_tensormap(&tm_x);
-        prefetch_tensormap(&tm_sfw);
-        prefetch_tensormap(&tm_sfx);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, 1);
+    // Set-up.  Warp 0 initialises the barriers and goes straight on to issue loads (it only
+    // arrives at the set-up barrier); the other warps wait there for the barriers and for the
+    // tensor-memory allocation made by warp 1.  This takes the set-up off the critical path of
+    // the first weight tiles, which matters for a kernel that runs for ~20 us.
+    if (warp == 0) {
+        if (elect_one_sync()) {
+            prefetch_tensormap(&tm_w);
+            prefetch_tensormap(&tm_x);
+            prefetch_tensormap(&tm_sfw);
+            prefetch_tensormap(&tm_sfx);
+            for (int s = 0; s < STAGES; ++s) {
+                mbar_init(bar_full + s * 8, 1);
+                mbar_init(bar_empty + s * 8, 1);
+            }
+            for (int a = 0; a < ACC; ++a) {
+                mbar_init(bar_tfull + a * 8, 1);
+                mbar_init(bar_tempty + a * 8, 4);
+            }
+            fence_mbar_init();
         }
-        for (int a = 0; a < ACC; ++a) {
-            mbar_init(bar_tfull + a * 8, 1);
-            mbar_init(bar_tempty + a * 8, 4);
+        __syncwarp();
+        asm volatile("bar.arrive 1, 192;" ::: "memory");
+    } else {
+        if (warp == 1) {
+            tmem_alloc<1>(tmem_ptr_smem, Cfg::kTmemCols);
+            tmem_relinquish<1>();
         }
-        fence_mbar_init();
+        tcgen05_fence_before();
+        asm volatile("bar.sync 1, 192;" ::: "memory");
+        tcgen05_fence_after();
     }
-    if (warp == 1) {
-        tmem_alloc<1>(tmem_ptr_smem, Cfg::kTmemCols);
-        tmem_relinquish<1>();
-    }
-    tcgen05_fence_before();
-    __syncthreads();
-    tcgen05_fence_after();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_gen, 0);
 
     if (warp == 0) {
@@ -132,8 +144,15 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long u = u_begin; u < u_end && ok;) {
-                const int g = (u_end - u < kBurst) ? static_cast<int>(u_end - u) : kBurst;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0);
+            int rec = 0;
+            // (tile, K block) of the next unit, advanced incrementally (no division in the loop)
+            int tile = static_cast<int>(u_begin / num_kb);
+            int kb = static_cast<int>(u_begin - static_cast<long long>(tile) * num_kb);
+            int left = static_cast<int>(u_end - u_begin);
+            while (left > 0 && ok) {
+                const long long t0 = tr ? clock64() : 0;
+                const int g = left < kBurst ? left : kBurst;
                 // slots are released in order, so a free last slot means the whole burst is free
                 const int last = stage + g - 1;
                 const int last_stage = last >= STAGES ? last - STAGES : last;
@@ -143,35 +162,48 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                     ok = false;
                     break;
                 }
-                int st[kBurst];
-                int tiles[kBurst];
-                int kbs[kBurst];
+                const long long t1 = tr ? clock64() : 0;
+                if (issuer) {
+                    // weight tiles first: neighbouring K blocks of the same rows go out back to back
+                    int s = stage, t = tile, k = kb;
 #pragma unroll
-                for (int i = 0; i < kBurst; ++i) {
-                    if (i < g) {
-                        st[i] = stage;
-                        tiles[i] = static_cast<int>((u + i) / num_kb);
-                        kbs[i] = static_cast<int>((u + i) - static_cast<long long>(tiles[i]) * num_kb);
-                        if (issuer) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kStageBytes);
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    for (int i = 0; i < kBurst; ++i) {
+                        if (i < g) {
+                            mbar_arrive_expect_tx(bar_full + s * 8, Cfg::kStageBytes);
+                            if (p.w_tile_major)
+                                tma_load_2d<1, 1>(smem_base + Cfg::kOffW + s * Cfg::kWBytes, &tm_w, bar_full + s * 8, 0,
+                                               (t * num_kb + k) * 128);
+                            else
+                                tma_load_2d<1, 1>(smem_base + Cfg::kOffW + s * Cfg::kWBytes, &tm_w, bar_full + s * 8, k * 128,
+                                               t * 128);
+                            if (++s == STAGES) s = 0;
+                            if (++k == num_kb) { k = 0; ++t; }
+                        }
+                    }
+                    s = stage; t = tile; k = kb;
+#pragma unroll
+                    for (int i = 0; i < kBurst; ++i) {
+                        if (i < g) {
+                            const uint32_t full = bar_full + s * 8;
+                            tma_load_2d<1, 1>(smem_base + Cfg::kOffSfw + s * Cfg::kSfBytes, &tm_sfw, full, 0,
+                                           t * p.w_sf_k_atoms + k * Cfg::kSfK);
+                            tma_load_2d<1, 2>(smem_base + Cfg::kOffX + s * Cfg::kXBytes, &tm_x, full, k * 128, 0);
+                            tma_load_2d<1, 2>(smem_base + Cfg::kOffSfx + s * Cfg::kSfBytes, &tm_sfx, full, 0, k * Cfg::kSfK);
+                            if (++s == STAGES) s = 0;
+                            if (++k == num_kb) { k = 0; ++t; }
+                        }
+                    }
+                    if (tr && rec < p.trace_cap) {
+                        long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
+                        r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = g;
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < kBurst; ++i)
-                    if (i < g && issuer)
-                        tma_load_2d<1>(smem_base + Cfg::kOffW + st[i] * Cfg::kWBytes, &tm_w, bar_full + st[i] * 8,
-                                       kbs[i] * 128, tiles[i] * 128);
-#pragma unroll
-                for (int i = 0; i < kBurst; ++i) {
-                    if (i < g && issuer) {
-                        const uint32_t full = bar_full + st[i] * 8;
-                        tma_load_2d<1>(smem_base + Cfg::kOffSfw + st[i] * Cfg::kSfBytes, &tm_sfw, full, 0,
-                                       tiles[i] * p.w_sf_k_atoms + kbs[i] * Cfg::kSfK);
-                        tma_load_2d<1>(smem_base + Cfg::kOffX + st[i] * Cfg::kXBytes, &tm_x, full, kbs[i] * 128, 0);
-                        tma_load_2d<1>(smem_base + Cfg::kOffSfx + st[i] * Cfg::kSfBytes, &tm_sfx, full, 0, kbs[i] * Cfg::kSfK);
-                    }
-                }
-                u += g;
+                ++rec;
+                left -= g;
+                stage += g;
+                if (stage >= STAGES) { stage -= STAGES; phase ^= 1u; }
+                kb += g;
+                while (kb >= num_kb) { kb -= num_kb; ++tile; }
             }
             if (ok) {
                 for (int i = 0; i < STAGES; ++i) {
@@ -193,6 +225,8 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             uint32_t phase = 0;
             int seg = 0;
             bool ok = true;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0);
+            int rec = 0;
             for (long long u = u_begin; u < u_end && ok; ++seg) {
                 const int kb0 = static_cast<int>(u % num_kb);
                 const long long left = u_end - u;
@@ -207,11 +241,13 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * MP;
                 for (int kb = kb0; kb < kb1; ++kb) {
+                    const long long t0 = tr ? clock64() : 0;
                     if (!mbar_wait(bar_full + stage * 8, phase)) {
                         if (issuer) atomicCAS(p.status, 0, kStatusTimeoutMma);
                         ok = false;
                         break;
                     }
+                    const long long t1 = tr ? clock64() : 0;
                     tcgen05_fence_after();
                     const uint64_t sfw_desc = make_desc_sf(smem_base + Cfg::kOffSfw + stage * Cfg::kSfBytes);
                     const uint64_t sfx_desc = make_desc_sf(smem_base + Cfg::kOffSfx + stage * Cfg::kSfBytes);
@@ -237,7 +273,12 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                                                             tmem_base + Cfg::kTmemSfx + sf_tile * 4, (j > 0) ? 1u : accum0);
                         }
                         tcgen05_commit<1>(bar_empty + stage * 8);
+                        if (tr && rec < p.trace_cap) {
+                            long long* r = p.trace + (1ll * p.trace_cap + rec) * 4;
+                            r[0] = t0; r[1] = t1; r[2] = clock64(); r[3] = kb;
+                        }
                     }
+                    ++rec;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (ok && issuer) tcgen05_commit<1>(bar_tfull + acc * 8);
@@ -262,11 +303,14 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             u += kb1 - kb0;
             const int acc = seg % ACC;
             const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
+            const bool tr = (p.trace != nullptr) && (blockIdx.x == 0) && (warp == 2) && (lane == 0) && (seg < p.trace_cap);
+            const long long te0 = tr ? clock64() : 0;
             if (!mbar_wait(bar_tfull + acc * 8, acc_phase)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
                 ok = false;
                 break;
             }
+            const long long te1 = tr ? clock64() : 0;
             tcgen05_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * MP;
             uint32_t v[MP];
@@ -278,6 +322,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + acc * 8);
 
+            const long long te2 = tr ? clock64() : 0;
             const int n = tile * 128 + n_local;
             const bool whole = (kb0 == 0 && kb1 == num_kb);
             if (whole) {
@@ -323,6 +368,10 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                             if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(sum[m] * alpha);
                     }
                 }
+            }
+            if (tr) {
+                long long* r = p.trace + (2ll * p.trace_cap + seg) * 4;
+                r[0] = te0; r[1] = te1; r[2] = te2; r[3] = clock64();
             }
         }
     }

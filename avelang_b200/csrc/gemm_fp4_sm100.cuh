@@ -50,7 +50,7 @@ struct GemmConfig {
     static constexpr int kBlockM = 128;                 // rows of A per CTA
     static constexpr int kBlockK = 256;                 // K elements per stage = 128 bytes
     static constexpr int kBnCta = BLOCK_N / CTA_GROUP;  // rows of B loaded by one CTA
-    static constexpr int kNb = BLOCK_N / 128;           // 128-row scale tiles across BLOCK_N
+    static constexpr int kNb = (BLOCK_N + 127) / 128;   // 128-row scale tiles covering BLOCK_N columns
     static constexpr int kSfK = kBlockK / SF_VEC / 4;   // scale tiles along K per stage (4 NVFP4, 2 MXFP4)
     static constexpr int kABytes = kBlockM * 128;
     static constexpr int kBBytes = kBnCta * 128;
@@ -59,7 +59,10 @@ struct GemmConfig {
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     static constexpr uint32_t kTxBytes = static_cast<uint32_t>(kStageBytes) * CTA_GROUP;
     static constexpr int kEpiWarps = 8;                 // two warps per TMEM lane quadrant
-    static constexpr int kEpiCols = BLOCK_N / 2;        // accumulator columns drained by one warp
+    static constexpr int kEpiGroups = BLOCK_N / 64;     // 64-column (128-byte) output groups per tile row
+    static constexpr int kEpiGroups0 = (kEpiGroups + 1) / 2;  // groups drained by the first warp of a quadrant
+    static constexpr int kEpiGroups1 = kEpiGroups / 2;        // ... and by the second
+    static constexpr int kEpiCols = kEpiGroups0 * 64;   // most accumulator columns one warp holds
     static constexpr int kEpiBufBytes = 32 * 128;       // 32 rows x 64 bf16, one per epilogue warp
     static constexpr int kEpiBytes = kEpiWarps * kEpiBufBytes;
     static constexpr int kOffA = 0;
@@ -77,7 +80,8 @@ struct GemmConfig {
     static constexpr int kTmemUsed = kTmemSfb + kSfK * kNb * 4;
     static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : kTmemUsed <= 256 ? 256 : 512;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
-    static_assert(BLOCK_N % 128 == 0 && BLOCK_N <= 256, "BLOCK_N must be 128 or 256");
+    static_assert(BLOCK_N % 64 == 0 && BLOCK_N >= 128 && BLOCK_N <= 256, "BLOCK_N must be 128, 192 or 256");
+    static_assert((BLOCK_N / CTA_GROUP) % 8 == 0, "each CTA's B tile must be whole 8-row swizzle groups");
     static_assert(kTmemUsed <= 512, "tensor memory budget");
     static_assert(kOffB % 1024 == 0 && kOffSfa % 1024 == 0 && kOffEpi % 1024 == 0, "swizzled tiles need 1024-byte alignment");
     static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -178,15 +182,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const uint32_t full = full0 + stage * 8;
                     if (issuer) {
                         if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
-                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
-                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
-                        tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
+                        tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
+                        tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
+                        tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
                                                sfa_atom0 + kb * Cfg::kSfK);
 #pragma unroll
                         for (int nb = 0; nb < Cfg::kNb; ++nb) {
-                            tma_load_2d<CTA_GROUP>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
+                            tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
                                                    &tm_sfb, full, 0,
-                                                   (tn * Cfg::kNb + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                                                   ((tn * BLOCK_N) / 128 + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
                         }
                         if (tr && rec < p.trace_cap) {
                             long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
@@ -233,6 +237,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + Cfg::kTmemAcc + acc * BLOCK_N;
+                // A tile that starts inside a 128-row scale tile (BLOCK_N = 192, odd tiles) reads its
+                // B scales from a column offset: 32 rows of B per TMEM column.
+                uint32_t sfb_shift = 0;
+                if constexpr (BLOCK_N % 128 != 0) {
+                    int tm, tn;
+                    decode_tile(t, p.tiles_m, p.tiles_n, tm, tn);
+                    sfb_shift = static_cast<uint32_t>(((tn * BLOCK_N) % 128) / 32);
+                }
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const long long t0 = tr ? (kb == 0 ? ta : clock64()) : 0;
                     if (!mbar_wait(bar_full + stage * 8, phase)) {
@@ -268,7 +280,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
                             mma_fp4_block_scaled<CTA_GROUP, SF_VEC>(
                                 d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
-                                tmem_base + Cfg::kTmemSfa + sf_tile * 4, tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4,
+                                tmem_base + Cfg::kTmemSfa + sf_tile * 4,
+                                tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4 + sfb_shift,
                                 (j > 0) ? 1u : accum0);
                         }
                         tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
@@ -293,7 +306,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (p.a_gs) alpha *= __ldg(p.a_gs);
         if (p.b_gs) alpha *= __ldg(p.b_gs);
         const uint32_t tempty0 = (CTA_GROUP == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
-        constexpr int kGroups = Cfg::kEpiCols / 64;   // 128-byte output line groups
+        const int my_groups = (half == 0) ? Cfg::kEpiGroups0 : Cfg::kEpiGroups1;   // warp-uniform
+        const int my_col = (half == 0) ? 0 : Cfg::kEpiGroups0 * 64;
         int tile_iter = 0;
         for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
             int tm, tn;
@@ -309,14 +323,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const long long te1 = tr ? clock64() : 0;
             tcgen05_fence_after();
             const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM + quad * 32;
-            const int col0 = tn * BLOCK_N + half * Cfg::kEpiCols;
-            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N +
-                                   half * Cfg::kEpiCols;
+            const int col0 = tn * BLOCK_N + my_col;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + Cfg::kTmemAcc + acc * BLOCK_N + my_col;
             // ---- drain: all of this warp's accumulator columns go to registers with the loads in
             // flight together (one round trip), then the accumulator is handed back at once
             uint32_t packed[Cfg::kEpiCols];
 #pragma unroll
-            for (int c = 0; c < Cfg::kEpiCols / 64; ++c) tmem_ld_32x32b_x64(t_acc + c * 64, &packed[c * 64]);
+            for (int c = 0; c < Cfg::kEpiGroups0; ++c)
+                if (c < my_groups) tmem_ld_32x32b_x64(t_acc + c * 64, &packed[c * 64]);
             tmem_ld_wait();
             tcgen05_fence_before();
             __syncwarp();
@@ -336,7 +350,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so
             // that every global store instruction writes four complete 128-byte lines
 #pragma unroll
-            for (int g = 0; g < kGroups; ++g) {
+            for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
+                if (g >= my_groups) break;
                 __syncwarp();
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -358,8 +373,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr) : "memory");
                     const int row = row0 + r;
                     if (row < p.m && col < p.n) {
-                        uint4* dst = reinterpret_cast<uint4*>(p.d + static_cast<size_t>(row) * p.ldd + col);
-                        *dst = make_uint4(w0, w1, w2, w3);
+                        // streaming store: the output is not re-read here and should not push the
+                        // operands (which other CTAs still need) out of L2
+                        __stcs(reinterpret_cast<uint4*>(p.d + static_cast<size_t>(row) * p.ldd + col), make_uint4(w0, w1, w2, w3));
                     }
                 }
             }

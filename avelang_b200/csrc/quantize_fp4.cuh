@@ -211,3 +211,29 @@ sf_to_tiled_kernel(const uint8_t* __restrict__ src, long long rows, long long co
 }
 
 }  // namespace avefp4
+
+namespace avefp4 {
+
+// Packed E2M1 weights, row-major (rows, k/2 bytes) -> tile-major: 16 KB tiles of 128 rows x 128
+// bytes (256 K elements), ordered [row block][K block], rows and K padded with zero bytes.  A
+// CTA that walks the K blocks of one row block then reads one contiguous stream from HBM.
+__global__ void __launch_bounds__(256)
+pack_weight_tiles_kernel(const uint8_t* __restrict__ src, long long rows, long long kbytes, uint8_t* __restrict__ dst) {
+    const long long kb_n = (kbytes + 127) / 128;
+    const long long rb_n = (rows + 127) / 128;
+    const long long total = rb_n * kb_n * 128 * 8;  // one thread per 16 bytes
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long c = i & 7;            // 16-byte chunk in the 128-byte row piece
+        const long long r = (i >> 3) & 127;   // row inside the tile
+        const long long tile = i >> 10;
+        const long long rb = tile / kb_n, kb = tile - rb * kb_n;
+        const long long row = rb * 128 + r;
+        const long long col = kb * 128 + c * 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows && col < kbytes) v = __ldg(reinterpret_cast<const uint4*>(src + row * kbytes + col));
+        *reinterpret_cast<uint4*>(dst + i * 16) = v;
+    }
+}
+
+}  // namespace avefp4

@@ -103,20 +103,41 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
+// L2 eviction-priority policies for TMA loads (the encodings createpolicy.fractional produces
+// for fraction 1.0): data read once is marked evict-first, data many CTAs re-read evict-last.
+constexpr uint64_t kL2EvictFirst = 0x12F0000000000000ull;
+constexpr uint64_t kL2EvictLast = 0x14F0000000000000ull;
+
 // 2-D tiled load global -> this CTA's shared memory, completion on `bar`.
 // CTA_GROUP == 2: `bar` may be a shared::cluster address in the pair's other CTA.
-template <int CTA_GROUP>
+// HINT: 0 = no cache hint, 1 = evict-first, 2 = evict-last.
+template <int CTA_GROUP, int HINT = 0>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y) {
-    if constexpr (CTA_GROUP == 1) {
-        asm volatile(
-            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-            ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
-            : "memory");
+    if constexpr (HINT == 0) {
+        if constexpr (CTA_GROUP == 1) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+                : "memory");
+        } else {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+                : "memory");
+        }
     } else {
-        asm volatile(
-            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-            ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
-            : "memory");
+        const uint64_t policy = (HINT == 1) ? kL2EvictFirst : kL2EvictLast;
+        if constexpr (CTA_GROUP == 1) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "l"(policy)
+                : "memory");
+        } else {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "l"(policy)
+                : "memory");
+        }
     }
 }
 

@@ -33,7 +33,9 @@ GEMM_1CTA_N128 = 1
 GEMM_1CTA_N256 = 2
 GEMM_2CTA_N256 = 3
 GEMM_2CTA_N128 = 4
+GEMM_2CTA_N192 = 5
 GEMM_SKINNY = 10
+GEMM_SKINNY_TILED_W = 11
 
 _BLOCK = {NVFP4: 16, MXFP4: 32}
 _FMT_NAME = {NVFP4: "NVFP4", MXFP4: "MXFP4"}
@@ -56,6 +58,7 @@ class Fp4Operand:
     rows: int
     k: int
     sf_layout: int = SF_TILED
+    tile_major: bool = False  # packed bytes re-ordered into 16 KB tiles by pack_weight_tiles (decode weights)
 
     @property
     def shape(self) -> tuple[int, int]:
@@ -158,6 +161,25 @@ def to_tiled(op: Fp4Operand) -> Fp4Operand:
     return Fp4Operand(op.packed, tiled, op.global_scale, op.fmt, op.rows, op.k, SF_TILED)
 
 
+def pack_weight_tiles(op: Fp4Operand) -> Fp4Operand:
+    """Offline re-packing of a weight operand for the decode (M <= 64) path.
+
+    The packed bytes are re-ordered into 16 KB tiles (128 rows x 256 K elements, row block major,
+    zero padded) so that the skinny kernel streams every weight row block from HBM as one
+    contiguous run.  The result can only be used as the B operand of a GEMM with M <= 64.
+    """
+    if op.tile_major:
+        return op
+    op = to_tiled(op)
+    dev = _require_cuda(op.packed, "packed")
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        nbytes = L.ave_fp4_weight_tiles_bytes(op.rows, op.k)
+        tiles = torch.empty((nbytes,), dtype=torch.uint8, device=op.packed.device)
+        _lib.check(L.ave_fp4_pack_weight_tiles(_ptr(op.packed.contiguous()), op.rows, op.k, _ptr(tiles), _stream(op.packed.device)))
+    return Fp4Operand(tiles, op.scales, op.global_scale, op.fmt, op.rows, op.k, SF_TILED, True)
+
+
 def make_operand(packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor | None, fmt: int,
                  sf_layout: int = SF_ROW_MAJOR) -> Fp4Operand:
     """Wrap tensors quantised elsewhere (e.g. offline weights) as an operand, checking shapes."""
@@ -221,6 +243,16 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
     if m == 0 or n == 0:
         return out
+    if A.tile_major:
+        raise ValueError("A must not be a tile-major (pack_weight_tiles) operand.")
+    if B.tile_major:
+        if m > 64:
+            raise ValueError(f"a tile-major weight operand serves only M <= 64, got M = {m}.")
+        if variant not in (GEMM_AUTO, GEMM_SKINNY, GEMM_SKINNY_TILED_W):
+            raise ValueError(f"a tile-major weight operand cannot be used with variant {variant}.")
+        variant = GEMM_SKINNY_TILED_W
+    elif variant == GEMM_SKINNY_TILED_W:
+        raise ValueError("variant GEMM_SKINNY_TILED_W needs a B operand made by pack_weight_tiles.")
     A = to_tiled(A)
     B = to_tiled(B)
     with torch.cuda.device(dev):

@@ -53,7 +53,9 @@ extern "C" {
 #define AVE_FP4_GEMM_1CTA_N256 2 /* 128x256 tile */
 #define AVE_FP4_GEMM_2CTA_N256 3 /* CTA pair, 256x256 tile */
 #define AVE_FP4_GEMM_2CTA_N128 4 /* CTA pair, 256x128 tile, two accumulator buffers */
+#define AVE_FP4_GEMM_2CTA_N192 5 /* CTA pair, 256x192 tile, two accumulator buffers */
 #define AVE_FP4_GEMM_SKINNY 10   /* M <= 64: operands swapped, stream-K over all SMs */
+#define AVE_FP4_GEMM_SKINNY_TILED_W 11 /* as 10, with b_packed in the tile-major layout of ave_fp4_pack_weight_tiles */
 
 /* Error codes returned as negative values. */
 #define AVE_FP4_ERR_ARG 1
@@ -105,6 +107,15 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
 int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, void* sf_tiled, void* stream);
 
 /*
+ * Offline weight packing for the decode path: packed E2M1 weights (n, k/2) row-major ->
+ * tile-major, 16 KB tiles of 128 rows x 128 bytes ordered [row block][K block], zero padded,
+ * ave_fp4_weight_tiles_bytes(n, k) bytes in total.  With this layout the skinny kernel reads
+ * each weight row block as one contiguous HBM stream.  No counterpart in the reference.
+ */
+int64_t ave_fp4_weight_tiles_bytes(int64_t n, int64_t k);
+int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k, void* packed_tiles, void* stream);
+
+/*
  * D (m, n) bf16, row stride ldd elements  =  A (m, k) * B (n, k)^T, fp32 accumulation,
  * result scaled by (*a_global_scale) * (*b_global_scale) (NULL = 1) and rounded to
  * bf16 (nearest even).  Scales in AVE_FP4_SF_TILED layout.
@@ -126,9 +137,9 @@ int ave_fp4_check(void* stream);
 
 /*
  * Profiling aid (no counterpart in the reference, whose only tracing is event timing in
- * benchmark/gemm/bench_amdgpu_gemm.py:43-52).  While a device buffer is set, the tiled GEMM
+ * benchmark/gemm/bench_amdgpu_gemm.py:43-52).  While a device buffer is set, the GEMM
  * kernels make CTA 0 record clock64() stamps: with cap = bytes / 96, record r of role q
- * (0 = TMA producer, 1 = MMA issuer, per K block; 2 = first epilogue warp, per tile) is four
+ * (0 = TMA producer, 1 = MMA issuer, per K block or load burst; 2 = first epilogue warp, per tile or segment) is four
  * int64 at buffer[(q * cap + r) * 4]: {before wait, after wait, after issue / drain, aux}.
  * Pass NULL to switch it off (the default).
  */

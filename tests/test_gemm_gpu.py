@@ -19,7 +19,7 @@ from conftest import GOLDEN
 pytestmark = pytest.mark.gpu
 
 REL_FRO_TOL = 1e-3
-TILED_VARIANTS = [ave.GEMM_1CTA_N128, ave.GEMM_1CTA_N256, ave.GEMM_2CTA_N256, ave.GEMM_2CTA_N128]
+TILED_VARIANTS = [ave.GEMM_1CTA_N128, ave.GEMM_1CTA_N256, ave.GEMM_2CTA_N256, ave.GEMM_2CTA_N128, ave.GEMM_2CTA_N192]
 
 
 def _bits(t):
@@ -72,7 +72,7 @@ def test_tiled_variants_match_oracle(cuda_device, oracle, fmt, variant, m, n, k)
 def test_ragged_shapes(cuda_device, oracle, fmt, m, n, k):
     """M, N not multiples of the tile and K not a multiple of the 256-element stage: edges are
     zero-filled on load and clipped on store."""
-    for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N256):
+    for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N256, ave.GEMM_2CTA_N192):
         _run_case(oracle, cuda_device, fmt, m, n, k, variant)
 
 
@@ -121,7 +121,7 @@ def test_small_golden_cases(cuda_device, oracle):
         fmt = int(g["fmt"])
         A = _to_dev((g["a_packed"], g["a_scales"], float(g["a_gs"])), fmt, cuda_device)
         B = _to_dev((g["b_packed"], g["b_scales"], float(g["b_gs"])), fmt, cuda_device)
-        for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N256, ave.GEMM_SKINNY):
+        for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N256, ave.GEMM_2CTA_N192, ave.GEMM_SKINNY):
             out = _gemm(A, B, fmt, variant=variant)
             ave.check_device_status(cuda_device)
             _check(out, g["d_bf16"], oracle, f"{name} variant {variant}")
@@ -178,7 +178,7 @@ def test_square_8192_full_size(cuda_device, oracle):
     slab = ave.Fp4Operand(A.packed[2048:2560], A.scales[2048:2560].contiguous(), A.global_scale, A.fmt, 512, k, ave.SF_ROW_MAJOR)
     d_slab = ave.gemm_nvfp4_transposed_b(slab, B)
     assert torch.equal(d_slab, d[2048:2560])
-    for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N128):
+    for variant in (ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N128, ave.GEMM_2CTA_N192, ave.GEMM_2CTA_N256):
         assert torch.equal(ave.gemm_nvfp4_transposed_b(A, B, variant=variant), d)
 
 
