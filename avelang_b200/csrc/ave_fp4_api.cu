@@ -262,7 +262,79 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
     return AVE_FP4_GEMM_2CTA_N256;
 }
 
+// ------------------------------------------------------------------------------------
+// Decode GEMM for callers that cannot allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc around a GEMM: a plugin that runs inside
+// another runtime's memory pool has no allocator of its own to ask, and a serving loop that
+// must never stall cannot afford the implicit device-wide synchronisation cudaMalloc/cudaFree
+// may cause.  For them the stream-K scratch of the skinny kernel lives in this fixed array,
+// which every GPU that loads the library holds (about 2.5 MiB) until the process exits.
+constexpr int kNoAllocMaxM = 16;          // one MMA-N step of activation rows
+constexpr int kNoAllocMaxN = 65536;       // 512 weight tiles
+constexpr int kNoAllocMaxCtas = 160;      // persistent CTAs (one per SM)
+constexpr size_t kNoAllocCounterBytes = (kNoAllocMaxN / 128) * 4 * sizeof(int);                   // 8 KiB
+constexpr size_t kNoAllocPartialBytes = static_cast<size_t>(kNoAllocMaxCtas) * 2 * 16 * 128 * 4;  // 2.5 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocCounterBytes + kNoAllocPartialBytes];
+
+// Device address of the array per device.  The array's name is only a host-side handle for the
+// symbol, so the address the kernel needs is looked up with cudaGetSymbolAddress, once per
+// device, while that device is current.
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_scratch_for_current_device(void** out) {
+    int dev = -1;
+    AVE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(-AVE_FP4_ERR_ARG, "device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        AVE_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (ptr == nullptr) return fail(-AVE_FP4_ERR_DEVICE, "cudaGetSymbolAddress returned a null scratch address");
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+
 }  // namespace
+
+extern "C" int ave_fp4_gemm_decode_noalloc(const void* a_packed, const void* a_scales, const void* a_global_scale,
+                                           const void* b_packed, const void* b_scales, const void* b_global_scale,
+                                           void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt,
+                                           void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
+    if (m < 0 || n < 0 || m > kNoAllocMaxM || n > kNoAllocMaxN)
+        return fail(-AVE_FP4_ERR_ARG,
+                    "ave_fp4_gemm_decode_noalloc: the built-in scratch serves M <= %d and N <= %d, got M = %lld, N = %lld; "
+                    "use ave_fp4_gemm with a caller-provided workspace for larger shapes",
+                    kNoAllocMaxM, kNoAllocMaxN, static_cast<long long>(m), static_cast<long long>(n));
+    if (ds->sm_count > kNoAllocMaxCtas)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: the built-in scratch serves at most %d SMs, this device has %d",
+                    kNoAllocMaxCtas, ds->sm_count);
+    if (m == 0 || n == 0) return 0;
+    if (k <= 0 || k % 32 != 0 || k > 0x7fffffff)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
+    if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: ldd must be >= N and a multiple of 8");
+    if (!a_packed || !a_scales || !b_packed || !b_scales || !d_bf16 || !aligned16(a_packed) || !aligned16(a_scales) ||
+        !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: null or misaligned (16-byte) pointer");
+    void* scratch = nullptr;
+    if ((rc = noalloc_scratch_for_current_device(&scratch))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left: the arrival counters must start at zero.
+    AVE_CUDA(cudaMemsetAsync(scratch, 0, skinny_counter_bytes(n), s));
+    const float* ags = static_cast<const float*>(a_global_scale);
+    const float* bgs = static_cast<const float*>(b_global_scale);
+    if (fmt == AVE_FP4_FMT_NVFP4)
+        return launch_skinny<16, 16, kStSkinny16>(*ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd,
+                                                  scratch, false, s);
+    return launch_skinny<16, 32, kStSkinny16>(*ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd,
+                                              scratch, false, s);
+}
 
 // ====================================================================================
 extern "C" {

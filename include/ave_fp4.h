@@ -128,6 +128,22 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Decode GEMM (M <= 16, N <= 65536) that allocates nothing and needs no caller workspace.
+ * It has no counterpart in the reference.  It exists for hosts that cannot call cudaMalloc:
+ * a plugin living inside another runtime's memory pool, or a serving loop that must not risk
+ * the device-wide stall an allocation can cause.  The stream-K scratch of the skinny kernel is
+ * a fixed array inside the library instead (about 2.5 MiB, held by every GPU that loads the
+ * library until the process exits).  Same arguments and result as ave_fp4_gemm with the skinny
+ * variant; shapes beyond the limits are rejected with an error, not served some other way.
+ * The first call on a device looks the array's device address up, so make that first call
+ * outside any stream capture.  All calls on one device share the array: calls that may overlap
+ * on the GPU (different streams) race on it and must be serialised by the caller.
+ */
+int ave_fp4_gemm_decode_noalloc(const void* a_packed, const void* a_scales, const void* a_global_scale,
+                                const void* b_packed, const void* b_scales, const void* b_global_scale, void* d_bf16,
+                                int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt, void* stream);
+
+/*
  * Synchronises `stream`, reads and clears the device status word of the current
  * device.  Returns 0 if every kernel since the last check ran to completion, or the
  * positive status code a kernel recorded when one of its bounded waits expired
