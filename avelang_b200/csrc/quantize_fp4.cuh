@@ -35,17 +35,29 @@ amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long 
                  unsigned int* __restrict__ amax_bits) {
     const long long groups_per_row = k / 8;
     const long long total = rows * groups_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     float a = 0.0f;
-    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < total;
-         g += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = g / groups_per_row;
-        const long long c = g - r * groups_per_row;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + c * 8));
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // four independent 128-bit loads in flight per thread
+    for (long long g0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g0 < total; g0 += 4 * stride) {
+        uint4 v[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            a = fmaxf(a, fabsf(__uint_as_float(w[i] << 16)));
-            a = fmaxf(a, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+        for (int u = 0; u < 4; ++u) {
+            const long long g = g0 + u * stride;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (g < total) {
+                const long long r = g / groups_per_row;
+                const long long c = g - r * groups_per_row;
+                v[u] = __ldcs(reinterpret_cast<const uint4*>(x + r * ldx + c * 8));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a = fmaxf(a, fabsf(__uint_as_float(w[i] << 16)));
+                a = fmaxf(a, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+            }
         }
     }
 #pragma unroll
@@ -82,6 +94,24 @@ __device__ __forceinline__ uint32_t pack8_e2m1(const float (&y)[8]) {
 //
 // amax_bits != nullptr: gs = amax / 2688 (1 when amax == 0), also stored to *gs_io.
 // amax_bits == nullptr: gs = *gs_io (caller-supplied static scale).
+// x / d for d > 0, bit-identical to IEEE division, at the cost of a multiply and two fused
+// multiply-adds: with r the correctly rounded reciprocal of d, q0 = RN(x*r) is within one ulp of
+// x/d, rem = x - q0*d is exact in an FMA, and RN(q0 + rem*r) is the correctly rounded quotient
+// (Markstein's theorem).  The theorem excludes a divisor whose significand is all ones, and the
+// reciprocal must neither overflow nor lose bits, so those divisors take the plain division.
+// The sign of a zero quotient is taken from x, as division would give.
+__device__ __forceinline__ bool divisor_is_plain(float d) {
+    const uint32_t b = __float_as_uint(d);
+    const uint32_t e = (b >> 23) & 0xffu;
+    return (b & 0x7fffffu) != 0x7fffffu && e >= 32u && e <= 222u;
+}
+
+__device__ __forceinline__ float div_by_recip(float x, float d, float r) {
+    const float q0 = __fmul_rn(x, r);
+    const float rem = __fmaf_rn(-q0, d, x);
+    return copysignf(__fmaf_rn(rem, r, q0), x);
+}
+
 template <int FMT, bool TILED>
 __global__ void __launch_bounds__(256)
 quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
@@ -102,27 +132,40 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             gs = *gs_io;
         }
     }
+    // a / 6 / gs is needed once per block; both divisors are fixed for the launch
+    const bool gs_plain = divisor_is_plain(gs);
+    const float gs_recip = __frcp_rn(gs);
+    const float sixth = __frcp_rn(6.0f);
 
-    const long long sf_cols = k / BLK;
-    const long long k_atoms = (sf_cols + 3) / 4;
+    const int kk = static_cast<int>(k);
+    const int sf_cols = kk / BLK;
+    const int k_atoms = (sf_cols + 3) / 4;
     const long long rows_pad = TILED ? ((rows + 127) / 128) * 128 : rows;
-    const long long k_pad = TILED ? k_atoms * 4 * BLK : k;
-    const long long chunks = (k_pad + 1023) / 1024;
+    const int k_pad = TILED ? k_atoms * 4 * BLK : kk;
+    const int chunks = (k_pad + 1023) / 1024;
     const long long items = rows_pad * chunks;
     const int quad_base = lane & ~3;
     const int qi = lane & 3;
 
     for (long long item = warp_global; item < items; item += warps_total) {
         const long long r = item / chunks;
-        const long long e0 = (item - r * chunks) * 1024;
+        const int e0 = static_cast<int>(item - r * chunks) * 1024;
+        const bool row_in = r < rows;
+        const __nv_bfloat16* xr = x + r * ldx;
+        // all four 128-bit loads of the step are in flight before any arithmetic
+        uint4 raw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e0 + (j * 32 + lane) * 8;
+            raw[j] = make_uint4(0, 0, 0, 0);
+            if (row_in && e < kk) raw[j] = __ldcs(reinterpret_cast<const uint4*>(xr + e));
+        }
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const long long e = e0 + (j * 32 + lane) * 8;
-            const bool in = (r < rows) && (e < k);
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (in) raw = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + e));
-            const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            const int e = e0 + (j * 32 + lane) * 8;
+            const bool in = row_in && (e < kk);
+            const uint32_t rw[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
             float v[8];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -138,12 +181,22 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             uint32_t code;
             float y[8];
             if (FMT == kFmtNvfp4) {
-                const float t = __fdiv_rn(a, 6.0f);
-                const float u = fminf(__fdiv_rn(t, gs), 448.0f);
+                // 6 is a plain divisor; a quotient in the subnormal range takes the plain division
+                const float t = (__float_as_uint(a) >= (32u << 23)) ? div_by_recip(a, 6.0f, sixth) : __fdiv_rn(a, 6.0f);
+                const float u = fminf(gs_plain ? div_by_recip(t, gs, gs_recip) : __fdiv_rn(t, gs), 448.0f);
                 code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
                 const float d = __fmul_rn(e4m3_decode(code), gs);
+                if (d == 0.0f) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = (d == 0.0f) ? copysignf(0.0f, v[i]) : __fdiv_rn(v[i], d);
+                    for (int i = 0; i < 8; ++i) y[i] = copysignf(0.0f, v[i]);
+                } else if (divisor_is_plain(d)) {
+                    const float rd = __frcp_rn(d);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = div_by_recip(v[i], d, rd);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = __fdiv_rn(v[i], d);
+                }
             } else {
                 if (a == 0.0f) {
                     code = 127u;
@@ -160,7 +213,7 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             // scale byte: one lane per block writes it
             const bool sf_writer = (FMT == kFmtNvfp4) ? ((lane & 1) == 0) : ((lane & 3) == 0);
             if (sf_writer && e < k_pad) {
-                const long long c = e / BLK;
+                const int c = e / BLK;
                 const uint8_t byte = in ? static_cast<uint8_t>(code) : static_cast<uint8_t>(0);
                 if (TILED) sf[sf_tiled_offset(r, c, k_atoms)] = byte;
                 else if (in) sf[r * sf_cols + c] = byte;
@@ -181,9 +234,9 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             else if (src == 2) o[2] = got;
             else o[3] = got;
         }
-        const long long e_out = e0 + (qi * 32 + quad_base) * 8;  // first element of this lane's 32-element run
-        if (r < rows && e_out < k) {
-            *reinterpret_cast<uint4*>(packed + r * (k / 2) + e_out / 2) = make_uint4(o[0], o[1], o[2], o[3]);
+        const int e_out = e0 + (qi * 32 + quad_base) * 8;  // first element of this lane's 32-element run
+        if (row_in && e_out < kk) {
+            __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e_out / 2), make_uint4(o[0], o[1], o[2], o[3]));
         }
     }
 }

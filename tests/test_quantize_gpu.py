@@ -119,3 +119,33 @@ def test_quantize_full_size_properties(cuda_device, oracle):
     assert np.array_equal(q.scales[rows.to(cuda_device)].cpu().numpy(), es)
     amax = x.float().abs().max().item()
     assert np.float32(gs.item()) == np.float32(np.float32(amax) / np.float32(2688.0))
+
+
+def test_quantize_full_8192_bit_exact(cuda_device, oracle):
+    """Every byte of the 8192 x 8192 quantise (67 M elements) against the C oracle, both formats."""
+    x = inputs.normal_bf16(8192, 8192, seed=0)
+    xd = x.to(cuda_device)
+    for fmt in (ave.NVFP4, ave.MXFP4):
+        q = _q(xd, fmt, ave.SF_ROW_MAJOR)
+        ep, es, eg = oracle.c_quantize(_bits(x), fmt)
+        assert np.array_equal(q.scales.cpu().numpy(), es)
+        assert np.array_equal(q.packed.cpu().numpy(), ep)
+
+
+@pytest.mark.parametrize("gs", [1.0, 0.0123, 5.9604645e-08 * 1.9999999, 1e-36, 3e-39, 1e30, 1.1754942e-38])
+def test_quantize_static_scales_fuzz(cuda_device, oracle, gs):
+    """Static tensor scales, including one whose significand is all ones, tiny, subnormal and huge ones,
+    on rows spanning 60 orders of magnitude: the division shortcuts must agree with IEEE division."""
+    rng = np.random.default_rng(1)
+    base = rng.standard_normal((512, 1024)).astype(np.float32)
+    row_scale = np.float32(10.0) ** rng.uniform(-30, 30, size=(512, 1)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        base *= row_scale * np.float32(gs if gs > 1e-30 else 1e-30)
+    base = np.clip(base, -3e38, 3e38)   # NaN / Inf inputs are outside the contract
+    x = torch.from_numpy(base).to(torch.bfloat16)
+    x[0] = 0
+    g = torch.tensor([gs], dtype=torch.float32, device=cuda_device)
+    q = ave.quantize_nvfp4(x.to(cuda_device), global_scale=g, sf_layout=ave.SF_ROW_MAJOR)
+    ep, es, _ = oracle.c_quantize(_bits(x), oracle.NVFP4, global_scale=float(np.float32(gs)))
+    assert np.array_equal(q.scales.cpu().numpy(), es)
+    assert np.array_equal(q.packed.cpu().numpy(), ep)
