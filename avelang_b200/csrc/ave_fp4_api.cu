@@ -152,7 +152,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // ----------------------------------------------------------------------------------
 template <int CG, int BN, int VEC, int ST, int ACC>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
-                const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream) {
+                const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
+                void* const* peers = nullptr, int n_peers = 0) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
@@ -172,6 +173,8 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.b_gs = bgs;
     p.d = static_cast<__nv_bfloat16*>(d);
     p.ldd = static_cast<int>(ldd);
+    p.n_peers = n_peers;
+    for (int i = 0; i < 7; ++i) p.peer_d[i] = (i < n_peers) ? static_cast<__nv_bfloat16*>(peers[i]) : nullptr;
     p.status = ds.status;
     p.trace = ds.trace;
     p.trace_cap = ds.trace_cap;
@@ -496,9 +499,10 @@ int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k
     return 0;
 }
 
-int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
-                 const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
-                 int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream) {
+static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                      const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                      int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
+                      void* const* peers, int n_peers) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
     if (rc) return rc;
@@ -517,7 +521,7 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
     const int v = resolve_variant(variant, m, n);
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
-#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers
     switch (v) {
         case AVE_FP4_GEMM_1CTA_N128:
             return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
@@ -530,6 +534,7 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
         case AVE_FP4_GEMM_2CTA_N192:
             return nv ? launch_gemm<2, 192, 16, kSt2N192, 2>(GEMM_ARGS) : launch_gemm<2, 192, 32, kSt2N192, 2>(GEMM_ARGS);
         case AVE_FP4_GEMM_SKINNY: {
+            if (n_peers > 0) return fail(-AVE_FP4_ERR_ARG, "the fused all-gather is served by the tiled kernels only (M > 64)");
             if (m > 64) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: the skinny variant needs M <= 64, got %lld", static_cast<long long>(m));
             const int64_t need = skinny_workspace_bytes(m, n, ds->sm_count);
             if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
@@ -561,6 +566,25 @@ int ave_fp4_set_trace(void* buffer, int64_t bytes) {
     ds->trace = static_cast<long long*>(buffer);
     ds->trace_cap = static_cast<int>(bytes / (3 * 4 * 8));
     return 0;
+}
+
+int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                 const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                 int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream) {
+    return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
+                      variant, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                           const void* b_scales, const void* b_global_scale, void* d_bf16, void* const* peer_d, int n_peers,
+                           int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt, int variant, void* stream) {
+    if (n_peers < 0 || n_peers > 7) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather: 0..7 peers supported, got %d", n_peers);
+    if (n_peers > 0 && peer_d == nullptr) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather: peer_d is NULL");
+    for (int i = 0; i < n_peers; ++i)
+        if (!peer_d[i] || !aligned16(peer_d[i])) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather: peer pointer %d is null or misaligned", i);
+    if (variant == AVE_FP4_GEMM_AUTO) variant = AVE_FP4_GEMM_2CTA_N256;
+    return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
+                      variant, nullptr, 0, stream, peer_d, n_peers);
 }
 
 int ave_fp4_check(void* stream) {

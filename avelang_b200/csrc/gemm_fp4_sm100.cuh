@@ -40,6 +40,8 @@ struct GemmParams {
     const float* b_gs;
     __nv_bfloat16* d;          // output, row stride ldd elements
     int ldd;
+    int n_peers;               // fused all-gather: the same tile is also stored to these buffers,
+    __nv_bfloat16* peer_d[7];  // which live in other GPUs' memory (peer-mapped), same layout as d
     int* status;               // device status word, written on a wait timeout
     long long* trace;          // optional clock64() stamps of CTA 0 (profiling aid), or nullptr
     int trace_cap;             // records per role; record r of role q at trace[(q * trace_cap + r) * 4 ..+3]
@@ -375,7 +377,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (row < p.m && col < p.n) {
                         // streaming store: the output is not re-read here and should not push the
                         // operands (which other CTAs still need) out of L2
-                        __stcs(reinterpret_cast<uint4*>(p.d + static_cast<size_t>(row) * p.ldd + col), make_uint4(w0, w1, w2, w3));
+                        const size_t off = static_cast<size_t>(row) * p.ldd + col;
+                        __stcs(reinterpret_cast<uint4*>(p.d + off), make_uint4(w0, w1, w2, w3));
+                        // fused all-gather: push the same 128-byte lines straight into every peer's copy
+                        // over NVLink (plain peer stores), so the exchange overlaps the next tiles' math
+                        for (int pi = 0; pi < p.n_peers; ++pi)
+                            __stcs(reinterpret_cast<uint4*>(p.peer_d[pi] + off), make_uint4(w0, w1, w2, w3));
                     }
                 }
             }

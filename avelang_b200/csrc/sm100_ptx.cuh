@@ -68,7 +68,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // Arrive on a barrier that may live in another CTA of the cluster (shared::cluster address).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    // default semantics (release at CTA scope): a cluster-scope release would first wait for this
+    // thread's earlier global stores, which the accumulator hand-over does not depend on
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {

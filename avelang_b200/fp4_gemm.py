@@ -211,7 +211,8 @@ def _workspace(L, device: torch.device, dev: int, m: int, n: int, k: int, fmt: i
     return ws
 
 
-def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int) -> torch.Tensor:
+def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int,
+          peer_ptrs: list[int] | None = None) -> torch.Tensor:
     name = _FMT_NAME[fmt]
     if A.fmt != fmt:
         raise ValueError(f"A must be an {name} operand, got {_FMT_NAME.get(A.fmt, A.fmt)}.")
@@ -257,6 +258,16 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
     B = to_tiled(B)
     with torch.cuda.device(dev):
         L = _lib.ensure_init(dev)
+        if peer_ptrs:
+            if m <= 64:
+                raise ValueError(f"the fused all-gather needs M > 64, got {m}.")
+            if len(peer_ptrs) > 7:
+                raise ValueError(f"at most 7 peers, got {len(peer_ptrs)}.")
+            arr = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+            _lib.check(L.ave_fp4_gemm_allgather(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed),
+                                                _ptr(B.scales), _ptr(B.global_scale), _ptr(out), arr, len(peer_ptrs), m, n, k,
+                                                out.stride(0), fmt, variant, _stream(A.device)))
+            return out
         ws = _workspace(L, A.device, dev, m, n, k, fmt, variant)
         _lib.check(L.ave_fp4_gemm(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
                                   _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt, variant, _ptr(ws),
@@ -274,6 +285,13 @@ def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | No
                             variant: int = GEMM_AUTO) -> torch.Tensor:
     """``out = A @ B.T`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
     return _gemm(A, B, out, MXFP4, variant)
+
+
+def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor, peer_ptrs: list[int],
+                                variant: int = GEMM_AUTO) -> torch.Tensor:
+    """``out = A @ B.T`` and, fused into the epilogue, the same tiles stored to ``peer_ptrs``: raw device
+    addresses (valid on this GPU) of the matching (M, N) block in every other rank's result buffer."""
+    return _gemm(A, B, out, A.fmt, variant, peer_ptrs)
 
 
 def check_device_status(device: torch.device | None = None) -> None:

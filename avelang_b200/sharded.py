@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from .fp4_gemm import Fp4Operand, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b, NVFP4
+from .fp4_gemm import Fp4Operand, gemm_allgather_transposed_b, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b, NVFP4
 
 
 def shard_bounds(n: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
@@ -58,27 +58,54 @@ class ShardedFp4Linear:
     shard dequantises exactly as the unsharded weight would.
     """
 
-    def __init__(self, weight_shard: Fp4Operand, group=None):
+    def __init__(self, weight_shard: Fp4Operand, group=None, fused: bool = False):
+        """fused=False: local GEMM, then NCCL all-gather.  fused=True: the GEMM epilogue stores every
+        output tile into all ranks' result buffers over NVLink (symmetric memory, plain peer stores),
+        so the exchange overlaps the math; a device-side barrier ends the step."""
         self.weight = weight_shard
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.fused = bool(fused) and self.world > 1
         self._gathered: torch.Tensor | None = None
+        self._hdl = None
+        self._peer_ptrs: list[int] = []
 
     def local_forward(self, x: Fp4Operand, out: torch.Tensor | None = None) -> torch.Tensor:
         fn = gemm_nvfp4_transposed_b if self.weight.fmt == NVFP4 else gemm_mxfp4_transposed_b
         return fn(x, self.weight, out=out)
 
-    def forward(self, x: Fp4Operand) -> torch.Tensor:
-        """Returns the gathered (world, M, N/world) bf16 result (the buffer is reused between calls).
+    def _buffers(self, m: int, n_local: int, device: torch.device) -> None:
+        shape = (self.world, m, n_local)
+        if self._gathered is not None and tuple(self._gathered.shape) == shape:
+            return
+        if self.fused:
+            import torch.distributed._symmetric_memory as symm
 
-        The local GEMM writes straight into this rank's slab of the gathered buffer and the
-        all-gather runs in place, so there is no staging copy.
+            self._gathered = symm.empty(shape, dtype=torch.bfloat16, device=device)
+            self._hdl = symm.rendezvous(self._gathered, self.group if self.group is not None else dist.group.WORLD)
+            slab_bytes = m * n_local * 2
+            # this rank's slab inside every other rank's buffer; start with the next rank so that
+            # the ranks do not all push to the same destination at once
+            order = [(self.rank + i) % self.world for i in range(1, self.world)]
+            self._peer_ptrs = [int(self._hdl.buffer_ptrs[p]) + self.rank * slab_bytes for p in order]
+        else:
+            self._gathered = torch.empty(shape, dtype=torch.bfloat16, device=device)
+
+    def forward(self, x: Fp4Operand) -> torch.Tensor:
+        """Returns the gathered (world, M, N/world) bf16 result (the buffer is reused between calls, so
+        every rank must be done reading the previous result before any rank calls forward again).
+
+        The local GEMM writes straight into this rank's slab of the gathered buffer; the exchange is
+        either an in-place NCCL all-gather or, with fused=True, part of the GEMM kernel itself.
         """
         m, n_local = x.rows, self.weight.rows
-        if self._gathered is None or tuple(self._gathered.shape) != (self.world, m, n_local):
-            self._gathered = torch.empty((self.world, m, n_local), dtype=torch.bfloat16, device=x.device)
+        self._buffers(m, n_local, x.device)
         local = self._gathered[self.rank]
+        if self.fused and m > 64:
+            gemm_allgather_transposed_b(x, self.weight, local, self._peer_ptrs)
+            self._hdl.barrier()
+            return self._gathered
         self.local_forward(x, out=local)
         if self.world > 1:
             dist.all_gather_into_tensor(self._gathered.view(-1, n_local), local, group=self.group)

@@ -60,45 +60,94 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs.
+
+    Uses NVML in a background thread (a sample every few milliseconds, so that even a timed
+    region of some tens of milliseconds is covered); falls back to an `nvidia-smi -lms` child
+    process when the NVML python binding is not importable.  Read-only queries.
+    """
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
+        self.rows = []          # (sm_mhz, sm_max_mhz, power_w, [hw_slowdown, hw_thermal, sw_thermal, sw_power_cap])
         self.proc = None
+        self.thread = None
+        self._stop = False
+        try:
+            import threading
+
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                    phys = int(ids[gpu_index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            smax = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            R = pynvml
+
+            def loop():
+                while not self._stop:
+                    try:
+                        mhz = float(R.nvmlDeviceGetClockInfo(h, R.NVML_CLOCK_SM))
+                        pw = R.nvmlDeviceGetPowerUsage(h) / 1000.0
+                        rs = R.nvmlDeviceGetCurrentClocksEventReasons(h) if hasattr(R, "nvmlDeviceGetCurrentClocksEventReasons") \
+                            else R.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                        flags = ["Active" if rs & m else "Not Active" for m in (
+                            R.nvmlClocksThrottleReasonHwSlowdown, R.nvmlClocksThrottleReasonHwThermalSlowdown,
+                            R.nvmlClocksThrottleReasonSwThermalSlowdown, R.nvmlClocksThrottleReasonSwPowerCap)]
+                        self.rows.append((mhz, smax, pw, flags))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(gpu_index)],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        rows = []
-        for line in out.splitlines():
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) >= 7:
-                try:
-                    rows.append((float(parts[0]), float(parts[1]), float(parts[2]), parts[3:7]))
-                except ValueError:
-                    pass
+        rows = self.rows
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+        elif self.proc is not None:
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                self.proc.kill()
+                out = ""
+            for line in out.splitlines():
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 7:
+                    try:
+                        rows.append((float(parts[0]), float(parts[1]), float(parts[2]), parts[3:7]))
+                    except ValueError:
+                        pass
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         pmax = max(r[2] for r in rows)
-        busy = [r for r in rows if r[2] >= 0.5 * pmax] or rows
+        busy = [r for r in rows if r[2] >= 0.6 * pmax] or rows
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({names[i] for r in busy for i in range(4) if r[3][i].lower().startswith("active")})
-        return {"sm_mhz": statistics.median(r[0] for r in busy), "sm_max_mhz": rows[0][1], "power_w_max": pmax,
-                "samples": len(busy), "reasons": reasons}
+        return {"sm_mhz": statistics.median(r[0] for r in busy), "sm_min_mhz": min(r[0] for r in busy),
+                "sm_max_mhz": rows[0][1], "power_w_max": round(pmax, 1), "samples": len(busy), "reasons": reasons,
+                "source": "nvml" if self.thread is not None else "nvidia-smi"}
 
 
 def dist_env():
@@ -156,7 +205,10 @@ def run_ours(args) -> dict:
         del a, b
     torch.cuda.synchronize(dev)
 
-    layers = [sharded.ShardedFp4Linear(B_ops[i]) for i in range(R)] if world > 1 else None
+    # N > 1: the exchange is fused into the GEMM epilogue (peer stores over NVLink); the NCCL
+    # all-gather path is timed next to it for comparison
+    fused = world > 1 and not args.nccl_allgather
+    layers = [sharded.ShardedFp4Linear(B_ops[i], fused=fused) for i in range(R)] if world > 1 else None
     outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
 
     def step(i: int):
@@ -190,11 +242,12 @@ def run_ours(args) -> dict:
     if world > 1:
         gemm_ms = timed(lambda i: ave.gemm_nvfp4_transposed_b(A_ops[i % R], B_ops[i % R], out=outs[i % 2]), args.steps,
                         3) / args.steps
-        gath = layers[0]._gathered
+        gath = torch.empty((world, M, N), dtype=torch.bfloat16, device=dev)
 
         def ag(i):
             dist.all_gather_into_tensor(gath.view(-1, N), gath[rank])
         ag_ms = timed(ag, max(5, args.steps // 2), 3) / max(5, args.steps // 2)
+        del gath
     else:
         gemm_ms, ag_ms = ms_per_step, None
     gemm_tflops = flops_per_gpu / (gemm_ms * 1e-3) / 1e12
@@ -215,10 +268,43 @@ def run_ours(args) -> dict:
         roofline["fused_step"] = {
             "target_ms": round(max(t_flop, t_link) * 1e3, 4), "achieved_ms": round(ms_per_step, 4),
             "frac": round(max(t_flop, t_link) * 1e3 / ms_per_step, 4), "bound": "nvlink" if t_link > t_flop else "tensor",
-            "gemm_only_ms": round(gemm_ms, 4), "allgather_only_ms": round(ag_ms, 4),
+            "exchange": "fused into the GEMM epilogue (peer stores) + device barrier" if fused else "NCCL all-gather after the GEMM",
+            "gemm_only_ms": round(gemm_ms, 4), "nccl_allgather_only_ms": round(ag_ms, 4),
+            "unfused_gemm_plus_nccl_ms": round(gemm_ms + ag_ms, 4),
             "gemm_only_tflops_per_gpu": round(gemm_tflops, 1),
             "allgather_busbw_gbs": round(nvlink_bytes / (ag_ms * 1e-3) / 1e9, 1),
         }
+
+    # ---- SM clock the GEMM really ran at: CTA 0 stamps clock64() through the library's trace hook
+    # during the last launch of a back-to-back burst; cycles / event time = effective MHz.  NVML samples
+    # lag behind a timed region of a few milliseconds, this does not.
+    try:
+        import ctypes
+
+        from avelang_b200 import _lib
+        L = _lib.ensure_init(local)
+        cap = 2048
+        tbuf = torch.zeros((3 * cap * 4,), dtype=torch.int64, device=dev)
+        _lib.check(L.ave_fp4_set_trace(ctypes.c_void_p(tbuf.data_ptr()), tbuf.numel() * 8))
+        for i in range(30):
+            ave.gemm_nvfp4_transposed_b(A_ops[i % R], B_ops[i % R], out=outs[i % 2])
+        t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0e.record()
+        ave.gemm_nvfp4_transposed_b(A_ops[0], B_ops[0], out=outs[0])
+        t1e.record()
+        torch.cuda.synchronize(dev)
+        _lib.check(L.ave_fp4_set_trace(None, 0))
+        tr = tbuf.cpu().view(3, cap, 4)
+        first = int(tr[0, 0, 0])
+        last = int(tr[2, :, 3].max())
+        if clocks is not None and first > 0 and last > first:
+            clocks["sm_mhz_in_kernel"] = round((last - first) / (t0e.elapsed_time(t1e) * 1e3), 1)
+            clocks["sm_mhz_in_kernel_how"] = "clock64 span of CTA 0 / CUDA-event time of the last of 31 back-to-back launches"
+        del tbuf
+    except Exception as exc:
+        if clocks is not None:
+            clocks["sm_mhz_in_kernel"] = None
+            clocks["sm_mhz_in_kernel_error"] = repr(exc)
 
     # ---- end to end through the public operators with host buffers
     host_d = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
@@ -248,7 +334,7 @@ def run_ours(args) -> dict:
         "config": {"workload": "c1_square_nvfp4_8192" if world == 1 else f"c1_per_gpu_slice_of_8192x{8192 * world}x8192_plus_allgather",
                    "m": M, "n_per_gpu": N, "k": K, "world": world,
                    "l2": f"{R} operand sets rotated; working set {R}x72 MB + 2x128 MB output > 126 MB L2",
-                   "parallelism": f"n-sharded x{world} + bf16 all-gather" if world > 1 else "single gpu"},
+                   "parallelism": (f"n-sharded x{world} + bf16 all-gather (" + ("fused peer stores" if fused else "nccl") + ")") if world > 1 else "single gpu"},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
         "pct_of_nominal_fp4_peak": round(100.0 * value / world / NOMINAL_FP4_TFLOPS, 2),
     }
@@ -423,6 +509,7 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=512, help="rows of A in the CPU baseline sample")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: exchange with NCCL after the GEMM instead of the fused epilogue")
     args = ap.parse_args()
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
     if res:

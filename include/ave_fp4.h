@@ -128,6 +128,20 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * GEMM fused with the all-gather of its output (N-sharded weights on one NVLink/NVSwitch box).
+ * As ave_fp4_gemm (tiled kernels, M > 64), and in addition every output tile is stored to
+ * peer_d[0 .. n_peers-1]: device pointers, valid on THIS GPU, to the same (m, n) block inside each
+ * other GPU's result buffer (peer-mapped memory, e.g. CUDA IPC / symmetric memory; same ldd).
+ * The stores are plain peer stores issued by the epilogue, so the exchange overlaps the remaining
+ * tiles' math.  The caller synchronises the ranks afterwards (all kernels done) before any rank
+ * reads its gathered buffer.  `peer_d` is a host array read during the call.  No counterpart in
+ * the reference, which has no multi-GPU code.
+ */
+int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                           const void* b_scales, const void* b_global_scale, void* d_bf16, void* const* peer_d, int n_peers,
+                           int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt, int variant, void* stream);
+
+/*
  * Decode GEMM (M <= 16, N <= 65536) that allocates nothing and needs no caller workspace.
  * It has no counterpart in the reference.  It exists for hosts that cannot call cudaMalloc:
  * a plugin living inside another runtime's memory pool, or a serving loop that must not risk
