@@ -147,6 +147,8 @@ int encode_sf(CUtensorMap* tm, const void* p, int64_t rows, int64_t k, int vec, 
                      CU_TENSOR_MAP_SWIZZLE_NONE, what);
 }
 
+constexpr int64_t kFusedSmallElems = 1 << 20;  // up to here amax + quantise run as one 8-CTA cluster launch
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ----------------------------------------------------------------------------------
@@ -214,7 +216,7 @@ int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
 template <int MP, int VEC, int ST>
 int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const float* xgs, const void* w, const void* sfw,
                   const float* wgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, void* workspace,
-                  bool w_tile_major, cudaStream_t stream) {
+                  bool w_tile_major, cudaStream_t stream, bool pdl = false) {
     using Cfg = SkinnyConfig<MP, VEC, ST>;
     CUtensorMap tm_w, tm_x, tm_sfw, tm_sfx;
     int rc;
@@ -239,6 +241,7 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.w_sf_k_atoms = static_cast<int>((k / VEC + 3) / 4);
     p.ldd = static_cast<int>(ldd);
     p.w_tile_major = w_tile_major ? 1 : 0;
+    p.pdl = pdl ? 1 : 0;
     p.x_gs = xgs;
     p.w_gs = wgs;
     p.d = static_cast<__nv_bfloat16*>(d);
@@ -251,13 +254,23 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     const long long units = static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
     long long grid = ds.sm_count;
     if (units < grid) grid = units;
-    gemm_fp4_skinny_kernel<MP, VEC, ST><<<static_cast<unsigned>(grid), 192, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_sfw,
-                                                                                                      tm_sfx, p);
-    AVE_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_skinny_kernel<MP, VEC, ST>, tm_w, tm_x, tm_sfw, tm_sfx, p));
     return 0;
 }
 
 int resolve_variant(int variant, int64_t m, int64_t n) {
+    variant &= ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS;
     if (variant == AVE_FP4_GEMM_SKINNY_TILED_W) return AVE_FP4_GEMM_SKINNY;
     if (variant != AVE_FP4_GEMM_AUTO) return variant;
     if (m <= 64) return AVE_FP4_GEMM_SKINNY;
@@ -461,6 +474,39 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
     return 0;
 }
 
+int ave_fp4_quantize_nvfp4_dynamic(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void* global_scale,
+                                   void* packed, void* scales, int sf_layout, void* amax_scratch, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (rows < 0 || k < 0 || k % 32 != 0 || ldx % 8 != 0 || ldx < k)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: need k %% 32 == 0 and ldx %% 8 == 0, ldx >= k");
+    if (rows == 0 || k == 0) return 0;
+    if (!global_scale) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: global_scale is NULL");
+    if (rows * k <= kFusedSmallElems) {
+        if (sf_layout != AVE_FP4_SF_ROW_MAJOR && sf_layout != AVE_FP4_SF_TILED)
+            return fail(-AVE_FP4_ERR_ARG, "unknown scale layout %d", sf_layout);
+        if (!x_bf16 || !packed || !scales || !aligned16(x_bf16) || !aligned16(packed))
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: null or misaligned pointer");
+        if (sf_layout == AVE_FP4_SF_TILED && (reinterpret_cast<uintptr_t>(scales) & 3u))
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: tiled scales must be 4-byte aligned");
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(x_bf16);
+        if (sf_layout == AVE_FP4_SF_TILED)
+            quantize_nvfp4_fused_small_kernel<true><<<kFusedClusterCtas, kFusedThreads, 0, s>>>(
+                x, rows, k, ldx, static_cast<float*>(global_scale), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales));
+        else
+            quantize_nvfp4_fused_small_kernel<false><<<kFusedClusterCtas, kFusedThreads, 0, s>>>(
+                x, rows, k, ldx, static_cast<float*>(global_scale), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales));
+        AVE_CUDA(cudaGetLastError());
+        return 0;
+    }
+    if (!amax_scratch) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: amax_scratch (4 bytes) is needed above %lld elements",
+                                   static_cast<long long>(kFusedSmallElems));
+    if ((rc = ave_fp4_amax(x_bf16, rows, k, ldx, amax_scratch, stream))) return rc;
+    return ave_fp4_quantize(x_bf16, rows, k, ldx, AVE_FP4_FMT_NVFP4, amax_scratch, global_scale, packed, scales, sf_layout, stream);
+}
+
 int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, void* sf_tiled, void* stream) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
@@ -540,7 +586,8 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
             if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
                 return fail(-AVE_FP4_ERR_WORKSPACE, "ave_fp4_gemm: workspace of %lld bytes (256-byte aligned, zero-initialised) required, got %lld",
                             static_cast<long long>(need), static_cast<long long>(workspace ? workspace_bytes : 0));
-#define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, variant == AVE_FP4_GEMM_SKINNY_TILED_W, s
+#define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, \
+    (variant & ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) == AVE_FP4_GEMM_SKINNY_TILED_W, s, (variant & AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) != 0
             const int mp = skinny_mp(m);
             if (mp == 16) return nv ? launch_skinny<16, 16, kStSkinny16>(SKINNY_ARGS) : launch_skinny<16, 32, kStSkinny16>(SKINNY_ARGS);
             if (mp == 32) return nv ? launch_skinny<32, 16, kStSkinny32>(SKINNY_ARGS) : launch_skinny<32, 32, kStSkinny32>(SKINNY_ARGS);

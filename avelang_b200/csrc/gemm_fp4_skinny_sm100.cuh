@@ -28,6 +28,8 @@ struct SkinnyParams {
     int tiles_n;          // ceil(N / 128)
     int w_sf_k_atoms;     // scale tiles along K
     int ldd;              // row stride of D in elements
+    int pdl;              // 1: launched with programmatic stream serialisation; weights may be read before the
+                          //    previous kernel in the stream has finished, everything else waits for it
     int w_tile_major;     // 0: W packed row-major (N, K/2); 1: 16 KB tiles [N/128][K/256][128 rows][128 B]
     const float* x_gs;    // device fp32 tensor scales or nullptr
     const float* w_gs;
@@ -136,6 +138,8 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         // the whole warp walks the loop (warp-uniform state); one elected lane issues
         {
             const bool issuer = elect_one_sync();
+            if (issuer) pdl_launch_dependents();
+            bool prior_done = (p.pdl == 0);
             // Loads are issued in bursts of kBurst consecutive K blocks: the weight tiles of a
             // burst are neighbouring 128-byte pieces of the same 128 rows, so DRAM sees
             // 512 contiguous bytes per row and page visit instead of 128.
@@ -179,6 +183,12 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                             if (++s == STAGES) s = 0;
                             if (++k == num_kb) { k = 0; ++t; }
                         }
+                    }
+                    // the activations (and their scales) may come from the previous kernel: wait for it
+                    // once, after the first weight tiles are already on their way
+                    if (!prior_done) {
+                        pdl_wait_prior_grid();
+                        prior_done = true;
                     }
                     s = stage; t = tile; k = kb;
 #pragma unroll
@@ -290,9 +300,12 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         // --------------------------------------------------------------- epilogue
         const int quad = warp & 3;
         const int n_local = quad * 32 + lane;
+        // everything this role reads (tensor scales) or writes (output, scratch) may be touched by the
+        // previous kernel in the stream
+        if (p.pdl) pdl_wait_prior_grid();
         float alpha = 1.0f;
-        if (p.x_gs) alpha *= __ldg(p.x_gs);
-        if (p.w_gs) alpha *= __ldg(p.w_gs);
+        if (p.x_gs) alpha *= __ldcg(p.x_gs);
+        if (p.w_gs) alpha *= __ldcg(p.w_gs);
         int seg = 0;
         bool ok = true;
         for (long long u = u_begin; u < u_end && ok; ++seg) {

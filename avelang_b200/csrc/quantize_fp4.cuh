@@ -112,26 +112,14 @@ __device__ __forceinline__ float div_by_recip(float x, float d, float r) {
     return copysignf(__fmaf_rn(rem, r, q0), x);
 }
 
+// The quantise loop shared by the kernels below: warp `warp_global` of `warps_total` takes the
+// 1024-element steps warp_global, warp_global + warps_total, ... of the (rows, k) matrix.
 template <int FMT, bool TILED>
-__global__ void __launch_bounds__(256)
-quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
-                    const unsigned int* __restrict__ amax_bits, float* __restrict__ gs_io,
-                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+__device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
+                                              float gs, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf,
+                                              long long warp_global, long long warps_total) {
     constexpr int BLK = (FMT == kFmtNvfp4) ? 16 : 32;
     const int lane = threadIdx.x & 31;
-    const long long warp_global = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-    const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-
-    float gs = 1.0f;
-    if (FMT == kFmtNvfp4) {
-        if (amax_bits != nullptr) {
-            const float amax = __uint_as_float(*amax_bits);
-            gs = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 2688.0f);
-            if (blockIdx.x == 0 && threadIdx.x == 0) *gs_io = gs;
-        } else {
-            gs = *gs_io;
-        }
-    }
     // a / 6 / gs is needed once per block; both divisors are fixed for the launch
     const bool gs_plain = divisor_is_plain(gs);
     const float gs_recip = __frcp_rn(gs);
@@ -151,6 +139,16 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
         const long long r = item / chunks;
         const int e0 = static_cast<int>(item - r * chunks) * 1024;
         const bool row_in = r < rows;
+        if (TILED && !row_in) {
+            // padding row of the tiled scale layout: nothing to load or pack, only zero scale bytes
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = e0 + (j * 32 + lane) * 8;
+                const bool sf_writer = (FMT == kFmtNvfp4) ? ((lane & 1) == 0) : ((lane & 3) == 0);
+                if (sf_writer && e < k_pad) sf[sf_tiled_offset(r, e / BLK, k_atoms)] = 0;
+            }
+            continue;
+        }
         const __nv_bfloat16* xr = x + r * ldx;
         // all four 128-bit loads of the step are in flight before any arithmetic
         uint4 raw[4];
@@ -239,6 +237,102 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e_out / 2), make_uint4(o[0], o[1], o[2], o[3]));
         }
     }
+}
+
+template <int FMT, bool TILED>
+__global__ void __launch_bounds__(256)
+quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
+                    const unsigned int* __restrict__ amax_bits, float* __restrict__ gs_io,
+                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+    // a kernel queued behind this one with programmatic stream serialisation may start its prologue now
+    // (it still waits for this grid to finish before it reads what is written here)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const long long warp_global = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    float gs = 1.0f;
+    if (FMT == kFmtNvfp4) {
+        if (amax_bits != nullptr) {
+            const float amax = __uint_as_float(*amax_bits);
+            gs = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 2688.0f);
+            if (blockIdx.x == 0 && threadIdx.x == 0) *gs_io = gs;
+        } else {
+            gs = *gs_io;
+        }
+    }
+    quantize_rows<FMT, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total);
+}
+
+// Small activations (decode: 16 x 8192): tensor amax and NVFP4 quantise in ONE launch of one
+// 8-CTA cluster.  Each CTA reduces its share of |x|, the eight partial maxima are exchanged through
+// distributed shared memory, and every CTA then quantises its share with the same tensor scale --
+// instead of a memset, an amax kernel and a quantise kernel (three launches on the decode path).
+constexpr int kFusedClusterCtas = 8;
+constexpr int kFusedThreads = 512;
+
+template <bool TILED>
+__global__ void __cluster_dims__(kFusedClusterCtas, 1, 1) __launch_bounds__(kFusedThreads)
+quantize_nvfp4_fused_small_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
+                                  float* __restrict__ gs_out, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+    __shared__ float s_warp[kFusedThreads / 32];
+    __shared__ float s_cta;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int tid = threadIdx.x;
+    const long long groups_per_row = k / 8;
+    const long long total = rows * groups_per_row;
+    const long long stride = static_cast<long long>(kFusedClusterCtas) * kFusedThreads;
+    float a = 0.0f;
+    for (long long g0 = static_cast<long long>(rank) * kFusedThreads + tid; g0 < total; g0 += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long g = g0 + u * stride;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (g < total) {
+                const long long r = g / groups_per_row;
+                v[u] = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + (g - r * groups_per_row) * 8));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a = fmaxf(a, fabsf(__uint_as_float(w[i] << 16)));
+                a = fmaxf(a, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if ((tid & 31) == 0) s_warp[tid >> 5] = a;
+    __syncthreads();
+    if (tid < 32) {
+        float b = (tid < kFusedThreads / 32) ? s_warp[tid] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+        if (tid == 0) s_cta = b;
+    }
+    // cluster barrier (release/acquire): every CTA's maximum is visible to the others afterwards
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float amax = 0.0f;
+    const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(&s_cta));
+#pragma unroll
+    for (int c = 0; c < kFusedClusterCtas; ++c) {
+        uint32_t remote;
+        float v;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(c));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+        amax = fmaxf(amax, v);
+    }
+    const float gs = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 2688.0f);
+    if (rank == 0 && tid == 0) *gs_out = gs;
+    const long long warp_global = (static_cast<long long>(rank) * kFusedThreads + tid) >> 5;
+    const long long warps_total = (static_cast<long long>(kFusedClusterCtas) * kFusedThreads) >> 5;
+    quantize_rows<kFmtNvfp4, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total);
+    // no CTA may exit while another can still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // Row-major (rows, cols) scale bytes -> 128x4 tiled layout (padding zero).

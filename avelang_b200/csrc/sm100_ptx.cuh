@@ -31,6 +31,12 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     return r;
 }
 
+// Programmatic dependent launch: let the next kernel in the stream start its prologue while this
+// one is still running / block until the previous kernel has completed and its writes are visible.
+// Both are no-ops when the launch did not opt in.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // One lane of the (fully active) warp gets true.
 __device__ __forceinline__ bool elect_one_sync() {
     uint32_t pred;

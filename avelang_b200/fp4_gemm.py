@@ -36,6 +36,7 @@ GEMM_2CTA_N128 = 4
 GEMM_2CTA_N192 = 5
 GEMM_SKINNY = 10
 GEMM_SKINNY_TILED_W = 11
+GEMM_FLAG_STATIC_WEIGHTS = 0x100
 
 _BLOCK = {NVFP4: 16, MXFP4: 32}
 _FMT_NAME = {NVFP4: "NVFP4", MXFP4: "MXFP4"}
@@ -118,9 +119,12 @@ def _quantize(x: torch.Tensor, fmt: int, global_scale: torch.Tensor | None, sf_l
         amax = None
         if fmt == NVFP4:
             if global_scale is None:
-                amax = torch.empty((1,), dtype=torch.float32, device=x.device)
-                gs = torch.empty((1,), dtype=torch.float32, device=x.device)
-                _lib.check(L.ave_fp4_amax(_ptr(x), rows, k, ldx, _ptr(amax), stream))
+                # tensor scale from the data: one fused launch for small inputs, amax + quantise otherwise
+                both = torch.empty((2,), dtype=torch.float32, device=x.device)
+                gs, amax = both[0:1], both[1:2]
+                _lib.check(L.ave_fp4_quantize_nvfp4_dynamic(_ptr(x), rows, k, ldx, _ptr(gs), _ptr(packed), _ptr(scales),
+                                                            sf_layout, _ptr(amax), stream))
+                return Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout)
             else:
                 if global_scale.dtype != torch.float32 or global_scale.numel() != 1:
                     raise ValueError("global_scale must be a float32 tensor with one element.")
@@ -212,7 +216,7 @@ def _workspace(L, device: torch.device, dev: int, m: int, n: int, k: int, fmt: i
 
 
 def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int,
-          peer_ptrs: list[int] | None = None) -> torch.Tensor:
+          peer_ptrs: list[int] | None = None, static_weights: bool = False) -> torch.Tensor:
     name = _FMT_NAME[fmt]
     if A.fmt != fmt:
         raise ValueError(f"A must be an {name} operand, got {_FMT_NAME.get(A.fmt, A.fmt)}.")
@@ -269,6 +273,8 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
                                                 out.stride(0), fmt, variant, _stream(A.device)))
             return out
         ws = _workspace(L, A.device, dev, m, n, k, fmt, variant)
+        if static_weights:
+            variant |= GEMM_FLAG_STATIC_WEIGHTS
         _lib.check(L.ave_fp4_gemm(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
                                   _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt, variant, _ptr(ws),
                                   0 if ws is None else ws.numel(), _stream(A.device)))
@@ -276,15 +282,19 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
 
 
 def gemm_nvfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
-                            variant: int = GEMM_AUTO) -> torch.Tensor:
-    """``out = A @ B.T`` for NVFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
-    return _gemm(A, B, out, NVFP4, variant)
+                            variant: int = GEMM_AUTO, static_weights: bool = False) -> torch.Tensor:
+    """``out = A @ B.T`` for NVFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out.
+
+    ``static_weights=True`` promises that B is not written by anything queued earlier on the stream; the
+    decode kernel (M <= 64) then overlaps its start-up and first weight loads with the previous kernel.
+    """
+    return _gemm(A, B, out, NVFP4, variant, static_weights=static_weights)
 
 
 def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
-                            variant: int = GEMM_AUTO) -> torch.Tensor:
+                            variant: int = GEMM_AUTO, static_weights: bool = False) -> torch.Tensor:
     """``out = A @ B.T`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
-    return _gemm(A, B, out, MXFP4, variant)
+    return _gemm(A, B, out, MXFP4, variant, static_weights=static_weights)
 
 
 def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor, peer_ptrs: list[int],

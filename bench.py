@@ -387,14 +387,19 @@ def decode_bench(ave, torch, dev, peaks) -> dict:
         return e0.elapsed_time(e1) / steps
 
     # plain launches are host-bound at this size, so replay a captured graph of 3 GEMMs (one per weight set)
+    ROUNDS = 4   # launches per captured graph = ROUNDS x 3 weight sets
+
     def three():
-        for W in Ws:
-            ave.gemm_nvfp4_transposed_b(X, W, out=out)
+        for _ in range(ROUNDS):
+            for W in Ws:
+                # weights are resident and never rewritten: the decode kernel may overlap its start-up with the previous launch
+                ave.gemm_nvfp4_transposed_b(X, W, out=out, static_weights=True)
 
     def chain():
-        for W in Ws:
-            q = ave.quantize_nvfp4(x)
-            ave.gemm_nvfp4_transposed_b(q, W, out=out)
+        for _ in range(ROUNDS):
+            for W in Ws:
+                q = ave.quantize_nvfp4(x)
+                ave.gemm_nvfp4_transposed_b(q, W, out=out, static_weights=True)
 
     res = {}
     for name, fn in (("gemm", three), ("chain", chain)):
@@ -405,14 +410,14 @@ def decode_bench(ave, torch, dev, peaks) -> dict:
         with torch.cuda.graph(g, stream=s):
             fn()
         torch.cuda.synchronize(dev)
-        ms = min(timed(lambda i: g.replay(), 30) for _ in range(3)) / 3.0
+        ms = min(timed(lambda i: g.replay(), 10) for _ in range(3)) / (3.0 * ROUNDS)
         res[name] = ms
     ave.check_device_status(dev)
     gbs = algo_bytes / (res["gemm"] * 1e-3) / 1e9
     return {"workload": "c2_decode_16x28672x8192_nvfp4", "gemm_us": round(res["gemm"] * 1e3, 2), "gbs": round(gbs, 1),
             "algorithmic_bytes": algo_bytes, "frac_of_measured_hbm": round(gbs / peaks["hbm"], 4),
             "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4),
-            "quantise_plus_gemm_us": round(res["chain"] * 1e3, 2), "timing": "CUDA graph of 3 launches (3 weight sets), replayed",
+            "quantise_plus_gemm_us": round(res["chain"] * 1e3, 2), "timing": "CUDA graph of 12 launches (4 rounds over 3 weight sets, programmatic dependent launch between them), replayed",
             "traffic": NCU_TRAFFIC_BYTES["decode"]}
 
 

@@ -57,6 +57,14 @@ extern "C" {
 #define AVE_FP4_GEMM_SKINNY 10   /* M <= 64: operands swapped, stream-K over all SMs */
 #define AVE_FP4_GEMM_SKINNY_TILED_W 11 /* as 10, with b_packed in the tile-major layout of ave_fp4_pack_weight_tiles */
 
+/*
+ * Flag, OR-ed into `variant`: the weight operand (b_packed, b_scales) is not written by any work queued
+ * earlier on `stream`.  The decode kernel is then launched with programmatic stream serialisation: it
+ * starts streaming weights while the previous kernel in the stream is still finishing and waits for it
+ * only before touching activations, scales, scratch or output.  Ignored by the tiled kernels.
+ */
+#define AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS 0x100
+
 /* Error codes returned as negative values. */
 #define AVE_FP4_ERR_ARG 1
 #define AVE_FP4_ERR_NOT_INIT 2
@@ -102,6 +110,15 @@ int ave_fp4_amax(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void*
  */
 int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, int fmt, const void* amax_f32,
                      void* global_scale, void* packed, void* scales, int sf_layout, void* stream);
+
+/*
+ * NVFP4 quantise with the tensor scale taken from the data (amax / 2688), in one call: for inputs of up
+ * to 2^20 elements (decode activations) one 8-CTA cluster launch does amax and quantise together; above
+ * that it is ave_fp4_amax + ave_fp4_quantize and needs `amax_scratch` (4 bytes of device memory).
+ * Results are identical to the two-call form.
+ */
+int ave_fp4_quantize_nvfp4_dynamic(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void* global_scale,
+                                   void* packed, void* scales, int sf_layout, void* amax_scratch, void* stream);
 
 /* Row-major (rows, cols) scale bytes -> tiled layout (for weights quantised elsewhere). */
 int ave_fp4_sf_to_tiled(const void* sf_row_major, int64_t rows, int64_t cols, void* sf_tiled, void* stream);
