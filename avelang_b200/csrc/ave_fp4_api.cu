@@ -450,6 +450,7 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: NVFP4 needs a global_scale pointer");
     if (sf_layout == AVE_FP4_SF_TILED && (reinterpret_cast<uintptr_t>(scales) & 3u))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: tiled scales must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(scales) & 1u) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize: scales must be 2-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool tiled = (sf_layout == AVE_FP4_SF_TILED);
     const long long rows_pad = tiled ? ((rows + 127) / 128) * 128 : rows;

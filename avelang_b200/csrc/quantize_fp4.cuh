@@ -6,13 +6,10 @@
 // fp32 step is a single round-to-nearest-even operation (explicit _rn intrinsics,
 // IEEE division), so packed nibbles and scale bytes are bit-identical.
 //
-// Mapping: a warp takes 1024 consecutive K elements of one row per step.  Lane L
-// loads four 128-bit groups (elements 8*(32*j+L) .. +7, j = 0..3), so every load
-// instruction of the warp is one contiguous 512-byte run.  The block maximum is
-// formed with warp shuffles (2 lanes per 16-element NVFP4 block, 4 lanes per
-// 32-element MXFP4 block).  Each lane packs its 8 values into one 32-bit word; a
-// 4x4 exchange inside each lane quad then gives every lane 16 contiguous output
-// bytes, written with one 128-bit store.
+// Mapping: a warp takes 1024 consecutive K elements of one row per step and lane L owns the 32
+// consecutive elements 32L .. 32L+31: four 128-bit loads, two whole 16-element NVFP4 blocks or one
+// 32-element MXFP4 block per lane (the block maximum stays inside the lane), one 128-bit store of
+// the 32 packed nibbles (512 contiguous bytes per warp) and one 16-bit or 8-bit scale store.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -112,8 +109,75 @@ __device__ __forceinline__ float div_by_recip(float x, float d, float r) {
     return copysignf(__fmaf_rn(rem, r, q0), x);
 }
 
+// One block of BLK consecutive elements held by a single lane: block maximum, scale code, then the
+// BLK elements divided by the block scale and packed, 8 nibbles per 32-bit word.
+template <int FMT>
+__device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ rw, float gs, bool gs_plain, float gs_recip,
+                                                   float sixth, uint32_t* __restrict__ out_words) {
+    constexpr int BLK = (FMT == kFmtNvfp4) ? 16 : 32;
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < BLK / 2; ++i) {
+        a = fmaxf(a, fabsf(__uint_as_float(rw[i] << 16)));
+        a = fmaxf(a, fabsf(__uint_as_float(rw[i] & 0xffff0000u)));
+    }
+    uint32_t code;
+    if (FMT == kFmtNvfp4) {
+        // 6 is a plain divisor; a quotient in the subnormal range takes the plain division
+        const float t = (__float_as_uint(a) >= (32u << 23)) ? div_by_recip(a, 6.0f, sixth) : __fdiv_rn(a, 6.0f);
+        const float u = fminf(gs_plain ? div_by_recip(t, gs, gs_recip) : __fdiv_rn(t, gs), 448.0f);
+        code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
+        const float d = __fmul_rn(e4m3_decode(code), gs);
+        const bool zero = (d == 0.0f);
+        const bool plain = divisor_is_plain(d);
+        const float rd = __frcp_rn(d);
+#pragma unroll
+        for (int w = 0; w < BLK / 8; ++w) {
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float lo = __uint_as_float(rw[w * 4 + i] << 16);
+                const float hi = __uint_as_float(rw[w * 4 + i] & 0xffff0000u);
+                if (zero) {
+                    y[2 * i] = copysignf(0.0f, lo);
+                    y[2 * i + 1] = copysignf(0.0f, hi);
+                } else if (plain) {
+                    y[2 * i] = div_by_recip(lo, d, rd);
+                    y[2 * i + 1] = div_by_recip(hi, d, rd);
+                } else {
+                    y[2 * i] = __fdiv_rn(lo, d);
+                    y[2 * i + 1] = __fdiv_rn(hi, d);
+                }
+            }
+            out_words[w] = pack8_e2m1(y);
+        }
+    } else {
+        if (a == 0.0f) {
+            code = 127u;
+        } else {
+            const int E = static_cast<int>((__float_as_uint(a) >> 23) & 0xffu);
+            code = static_cast<uint32_t>(max(E - 2, 0));
+        }
+        const float inv = __uint_as_float((254u - code) << 23);  // 2^(127-code), exact scaling
+#pragma unroll
+        for (int w = 0; w < BLK / 8; ++w) {
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[2 * i] = __fmul_rn(__uint_as_float(rw[w * 4 + i] << 16), inv);
+                y[2 * i + 1] = __fmul_rn(__uint_as_float(rw[w * 4 + i] & 0xffff0000u), inv);
+            }
+            out_words[w] = pack8_e2m1(y);
+        }
+    }
+    return code;
+}
+
 // The quantise loop shared by the kernels below: warp `warp_global` of `warps_total` takes the
-// 1024-element steps warp_global, warp_global + warps_total, ... of the (rows, k) matrix.
+// 1024-element steps warp_global, warp_global + warps_total, ... of the (rows, k) matrix.  Inside a
+// step lane L owns the 32 consecutive elements 32L .. 32L+31: four 128-bit loads (64 contiguous bytes),
+// two whole NVFP4 blocks or one MXFP4 block (so a block maximum needs no exchange between lanes),
+// one 128-bit store of 32 nibbles and one 16-bit / 8-bit scale store.
 template <int FMT, bool TILED>
 __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
                                               float gs, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf,
@@ -132,110 +196,41 @@ __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ 
     const int k_pad = TILED ? k_atoms * 4 * BLK : kk;
     const int chunks = (k_pad + 1023) / 1024;
     const long long items = rows_pad * chunks;
-    const int quad_base = lane & ~3;
-    const int qi = lane & 3;
 
     for (long long item = warp_global; item < items; item += warps_total) {
         const long long r = item / chunks;
-        const int e0 = static_cast<int>(item - r * chunks) * 1024;
-        const bool row_in = r < rows;
-        if (TILED && !row_in) {
-            // padding row of the tiled scale layout: nothing to load or pack, only zero scale bytes
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int e = e0 + (j * 32 + lane) * 8;
-                const bool sf_writer = (FMT == kFmtNvfp4) ? ((lane & 1) == 0) : ((lane & 3) == 0);
-                if (sf_writer && e < k_pad) sf[sf_tiled_offset(r, e / BLK, k_atoms)] = 0;
+        const int e = static_cast<int>(item - r * chunks) * 1024 + lane * 32;   // this lane's first element
+        const int c = e / BLK;                                                  // ... and first scale column
+        const bool in = (r < rows) && (e < kk);
+        if (!in) {
+            // padding of the tiled scale layout (rows up to a multiple of 128, columns of 4): zero bytes
+            if (TILED && e < k_pad) {
+                uint8_t* p = sf + sf_tiled_offset(r, c, k_atoms);
+                if (FMT == kFmtNvfp4) *reinterpret_cast<uint16_t*>(p) = 0;
+                else *p = 0;
             }
             continue;
         }
-        const __nv_bfloat16* xr = x + r * ldx;
-        // all four 128-bit loads of the step are in flight before any arithmetic
-        uint4 raw[4];
+        const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + e);
+        uint32_t rw[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = e0 + (j * 32 + lane) * 8;
-            raw[j] = make_uint4(0, 0, 0, 0);
-            if (row_in && e < kk) raw[j] = __ldcs(reinterpret_cast<const uint4*>(xr + e));
+        for (int i = 0; i < 4; ++i) {
+            const uint4 v = __ldg(src + i);
+            rw[4 * i] = v.x; rw[4 * i + 1] = v.y; rw[4 * i + 2] = v.z; rw[4 * i + 3] = v.w;
         }
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = e0 + (j * 32 + lane) * 8;
-            const bool in = row_in && (e < kk);
-            const uint32_t rw[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                v[2 * i] = __uint_as_float(rw[i] << 16);
-                v[2 * i + 1] = __uint_as_float(rw[i] & 0xffff0000u);
-            }
-            float a = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(v[i]));
-            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-            if (FMT == kFmtMxfp4) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-
-            uint32_t code;
-            float y[8];
-            if (FMT == kFmtNvfp4) {
-                // 6 is a plain divisor; a quotient in the subnormal range takes the plain division
-                const float t = (__float_as_uint(a) >= (32u << 23)) ? div_by_recip(a, 6.0f, sixth) : __fdiv_rn(a, 6.0f);
-                const float u = fminf(gs_plain ? div_by_recip(t, gs, gs_recip) : __fdiv_rn(t, gs), 448.0f);
-                code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
-                const float d = __fmul_rn(e4m3_decode(code), gs);
-                if (d == 0.0f) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = copysignf(0.0f, v[i]);
-                } else if (divisor_is_plain(d)) {
-                    const float rd = __frcp_rn(d);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = div_by_recip(v[i], d, rd);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = __fdiv_rn(v[i], d);
-                }
-            } else {
-                if (a == 0.0f) {
-                    code = 127u;
-                } else {
-                    const int E = static_cast<int>((__float_as_uint(a) >> 23) & 0xffu);
-                    code = static_cast<uint32_t>(max(E - 2, 0));
-                }
-                const float inv = __uint_as_float((254u - code) << 23);  // 2^(127-code), exact scaling
-#pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(v[i], inv);
-            }
-            w[j] = pack8_e2m1(y);
-
-            // scale byte: one lane per block writes it
-            const bool sf_writer = (FMT == kFmtNvfp4) ? ((lane & 1) == 0) : ((lane & 3) == 0);
-            if (sf_writer && e < k_pad) {
-                const int c = e / BLK;
-                const uint8_t byte = in ? static_cast<uint8_t>(code) : static_cast<uint8_t>(0);
-                if (TILED) sf[sf_tiled_offset(r, c, k_atoms)] = byte;
-                else if (in) sf[r * sf_cols + c] = byte;
-            }
-        }
-        // 4x4 exchange inside each quad: lane q ends up with word q of all four lanes,
-        // i.e. the 16 contiguous output bytes of 32 consecutive elements of segment q.
         uint32_t o[4];
-#pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
-            const int send_idx = (qi + rr) & 3;
-            const uint32_t send = send_idx == 0 ? w[0] : send_idx == 1 ? w[1] : send_idx == 2 ? w[2] : w[3];
-            const int src = (qi - rr) & 3;
-            const uint32_t got = __shfl_sync(0xffffffffu, send, quad_base + src);
-            // value received is word `qi` of lane `src`
-            if (src == 0) o[0] = got;
-            else if (src == 1) o[1] = got;
-            else if (src == 2) o[2] = got;
-            else o[3] = got;
+        uint32_t codes;
+        if (FMT == kFmtNvfp4) {
+            const uint32_t c0 = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
+            const uint32_t c1 = quantize_block<FMT>(rw + 8, gs, gs_plain, gs_recip, sixth, o + 2);
+            codes = c0 | (c1 << 8);
+        } else {
+            codes = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
         }
-        const int e_out = e0 + (qi * 32 + quad_base) * 8;  // first element of this lane's 32-element run
-        if (row_in && e_out < kk) {
-            __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e_out / 2), make_uint4(o[0], o[1], o[2], o[3]));
-        }
+        __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e / 2), make_uint4(o[0], o[1], o[2], o[3]));
+        uint8_t* p = TILED ? sf + sf_tiled_offset(r, c, k_atoms) : sf + r * sf_cols + c;
+        if (FMT == kFmtNvfp4) *reinterpret_cast<uint16_t*>(p) = static_cast<uint16_t>(codes);   // columns c, c+1 (c even)
+        else *p = static_cast<uint8_t>(codes);
     }
 }
 

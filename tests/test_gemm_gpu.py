@@ -204,3 +204,53 @@ def test_mxfp4_heavy_tail_2048(cuda_device, oracle):
     """The MXFP4 config's distributions (Student-t activations, N(0, 0.02) weights) on a 2048^3
     sub-problem the oracle finishes in seconds."""
     _run_case(oracle, cuda_device, ave.MXFP4, 2048, 2048, 2048, ave.GEMM_AUTO, a_kind="student_t3", b_kind="weight")
+
+
+def test_tile_major_weights_match_row_major(cuda_device, oracle):
+    """Weights re-packed into 16 KB tiles for the decode path give the same bits as row-major weights,
+    including ragged N and a K that is not a multiple of the 256-element tile."""
+    for fmt, m, n, k in ((ave.NVFP4, 16, 4096, 8192), (ave.MXFP4, 7, 1160, 2080), (ave.NVFP4, 64, 136, 96)):
+        quant = ave.quantize_nvfp4 if fmt == ave.NVFP4 else ave.quantize_mxfp4
+        X = quant(inputs.outlier_activations_bf16(m, k, 0).to(cuda_device))
+        W = quant(inputs.normal_bf16(n, k, 1, std=0.02).to(cuda_device))
+        Wt = ave.pack_weight_tiles(W)
+        assert Wt.tile_major and Wt.packed.numel() == ((n + 127) // 128) * ((k + 255) // 256) * 16384
+        d0 = _gemm(X, W, fmt)
+        d1 = _gemm(X, Wt, fmt)
+        ave.check_device_status(cuda_device)
+        assert torch.equal(d0, d1)
+    big = ave.quantize_nvfp4(inputs.normal_bf16(128, 256, 2).to(cuda_device))
+    with pytest.raises(ValueError, match="M <= 64"):
+        ave.gemm_nvfp4_transposed_b(big, ave.pack_weight_tiles(big))
+
+
+def test_static_weights_overlap_keeps_results(cuda_device, oracle):
+    """With static_weights=True the decode kernel starts before its predecessor in the stream has
+    finished.  Activations quantised by that predecessor, the shared scratch and the output must
+    still be handled in order: a chain of quantise -> GEMM steps with fresh activations every step
+    gives exactly the results of the fully serialised form."""
+    m, n, k = 16, 8192, 4096
+    W = ave.quantize_nvfp4(inputs.normal_bf16(n, k, 1, std=0.02).to(cuda_device))
+    xs = [inputs.outlier_activations_bf16(m, k, 10 + i).to(cuda_device) for i in range(8)]
+    want = [ave.gemm_nvfp4_transposed_b(ave.quantize_nvfp4(x), W).clone() for x in xs]
+    torch.cuda.synchronize()
+    outs = [torch.empty((m, n), dtype=torch.bfloat16, device=cuda_device) for _ in xs]
+    for _ in range(3):
+        for x, o in zip(xs, outs):
+            ave.gemm_nvfp4_transposed_b(ave.quantize_nvfp4(x), W, out=o, static_weights=True)
+        ave.check_device_status(cuda_device)
+        for o, w in zip(outs, want):
+            assert torch.equal(o, w)
+    # and inside a captured graph, the way the benchmark replays it
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=s):
+        for x, o in zip(xs, outs):
+            ave.gemm_nvfp4_transposed_b(ave.quantize_nvfp4(x), W, out=o, static_weights=True)
+    for o in outs:
+        o.zero_()
+    for _ in range(3):
+        g.replay()
+    ave.check_device_status(cuda_device)
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
