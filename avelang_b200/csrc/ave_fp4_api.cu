@@ -79,6 +79,7 @@ cudaError_t prepare_skinny() {
 
 // Stage counts per tile shape (shared-memory budget 227 KB per CTA).
 constexpr int kSt1N128 = 5, kSt1N256 = 3, kSt2N256 = 5, kSt2N128 = 6, kSt2N192 = 5;
+constexpr int kStDense2N256 = 6, kStDense1N128 = 6;   // dense bf16: 32 KB per stage
 constexpr int kStSkinny16 = 8, kStSkinny32 = 8, kStSkinny64 = 7;
 
 cudaError_t prepare_all() {
@@ -94,6 +95,8 @@ cudaError_t prepare_all() {
     PREP((prepare_gemm<2, 192, 32, kSt2N192, 2>()));
     PREP((prepare_gemm<2, 128, 16, kSt2N128, 2>()));
     PREP((prepare_gemm<2, 128, 32, kSt2N128, 2>()));
+    PREP((prepare_gemm<2, 256, 0, kStDense2N256, 2>()));
+    PREP((prepare_gemm<1, 128, 0, kStDense1N128, 2>()));
     PREP((prepare_skinny<16, 16, kStSkinny16>()));
     PREP((prepare_skinny<16, 32, kStSkinny16>()));
     PREP((prepare_skinny<32, 16, kStSkinny32>()));
@@ -199,6 +202,53 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+    return 0;
+}
+
+// Dense bf16 operands (the reference operator's own data type): same kernel, no scale factors.
+template <int CG, int BN, int ST, int ACC>
+int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd,
+                 cudaStream_t stream) {
+    using Cfg = GemmConfig<CG, BN, 0, ST, ACC>;
+    CUtensorMap tm_a, tm_b;
+    int rc;
+    // bf16 rows seen as bytes: K * 2 bytes per row, 128-byte (64-element) boxes, 128-byte swizzle
+    if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(m),
+                        static_cast<uint64_t>(k) * 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B, "A")))
+        return rc;
+    if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b, static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(n),
+                        static_cast<uint64_t>(k) * 2, 128, Cfg::kBnCta, CU_TENSOR_MAP_SWIZZLE_128B, "B")))
+        return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.tiles_m = static_cast<int>((m + 128 * CG - 1) / (128 * CG));
+    p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = static_cast<int>(ldd);
+    p.status = ds.status;
+    p.trace = ds.trace;
+    p.trace_cap = ds.trace_cap;
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    long long clusters = ds.sm_count / CG;
+    if (tiles < clusters) clusters = tiles;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * CG), 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // the scale-factor tensor maps are unused in dense mode; pass copies of the operand maps
+    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, 0, ST, ACC>, tm_a, tm_b, tm_a, tm_b, p));
     return 0;
 }
 
@@ -633,6 +683,30 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
     if (variant == AVE_FP4_GEMM_AUTO) variant = AVE_FP4_GEMM_2CTA_N256;
     return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
                       variant, nullptr, 0, stream, peer_d, n_peers);
+}
+
+int ave_bf16_gemm(const void* a_bf16, const void* b_bf16, void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd,
+                  int variant, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (m < 0 || n < 0 || k < 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x3fffffff)
+        return fail(-AVE_FP4_ERR_ARG, "ave_bf16_gemm: size out of range");
+    if (m == 0 || n == 0) return 0;
+    if (k == 0 || k % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_bf16_gemm: K must be a positive multiple of 8, got %lld", static_cast<long long>(k));
+    if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_bf16_gemm: ldd must be >= N and a multiple of 8, got %lld", static_cast<long long>(ldd));
+    if (!a_bf16 || !b_bf16 || !d_bf16 || !aligned16(a_bf16) || !aligned16(b_bf16) || !aligned16(d_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_bf16_gemm: null or misaligned (16-byte) pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (variant) {
+        case AVE_FP4_GEMM_AUTO:
+        case AVE_FP4_GEMM_2CTA_N256:
+            return launch_dense<2, 256, kStDense2N256, 2>(*ds, a_bf16, b_bf16, d_bf16, m, n, k, ldd, s);
+        case AVE_FP4_GEMM_1CTA_N128:
+            return launch_dense<1, 128, kStDense1N128, 2>(*ds, a_bf16, b_bf16, d_bf16, m, n, k, ldd, s);
+        default:
+            return fail(-AVE_FP4_ERR_ARG, "ave_bf16_gemm: variant %d is not built for bf16 operands", variant);
+    }
 }
 
 int ave_fp4_check(void* stream) {

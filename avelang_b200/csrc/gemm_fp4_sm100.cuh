@@ -50,10 +50,11 @@ struct GemmParams {
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
 struct GemmConfig {
     static constexpr int kBlockM = 128;                 // rows of A per CTA
-    static constexpr int kBlockK = 256;                 // K elements per stage = 128 bytes
+    static constexpr bool kDense = (SF_VEC == 0);       // SF_VEC 0: dense bf16 operands, no scale factors
+    static constexpr int kBlockK = kDense ? 64 : 256;   // K elements per stage = 128 bytes
     static constexpr int kBnCta = BLOCK_N / CTA_GROUP;  // rows of B loaded by one CTA
     static constexpr int kNb = (BLOCK_N + 127) / 128;   // 128-row scale tiles covering BLOCK_N columns
-    static constexpr int kSfK = kBlockK / SF_VEC / 4;   // scale tiles along K per stage (4 NVFP4, 2 MXFP4)
+    static constexpr int kSfK = kDense ? 0 : kBlockK / (kDense ? 1 : SF_VEC) / 4;   // scale tiles along K per stage (4 NVFP4, 2 MXFP4)
     static constexpr int kABytes = kBlockM * 128;
     static constexpr int kBBytes = kBnCta * 128;
     static constexpr int kSfaBytes = kSfK * 512;
@@ -186,13 +187,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, Cfg::kTxBytes);
                         tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffA + stage * Cfg::kABytes, &tm_a, full, kb * 128, row_a);
                         tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffB + stage * Cfg::kBBytes, &tm_b, full, kb * 128, row_b);
-                        tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
-                                               sfa_atom0 + kb * Cfg::kSfK);
+                        if constexpr (!Cfg::kDense) {
+                            tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfa + stage * Cfg::kSfaBytes, &tm_sfa, full, 0,
+                                                   sfa_atom0 + kb * Cfg::kSfK);
 #pragma unroll
-                        for (int nb = 0; nb < Cfg::kNb; ++nb) {
-                            tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
-                                                   &tm_sfb, full, 0,
-                                                   ((tn * BLOCK_N) / 128 + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                            for (int nb = 0; nb < Cfg::kNb; ++nb) {
+                                tma_load_2d<CTA_GROUP, 2>(smem_base + Cfg::kOffSfb + stage * Cfg::kSfbBytes + nb * Cfg::kSfK * 512,
+                                                       &tm_sfb, full, 0,
+                                                       ((tn * BLOCK_N) / 128 + nb) * p.sf_k_atoms + kb * Cfg::kSfK);
+                            }
                         }
                         if (tr && rec < p.trace_cap) {
                             long long* r = p.trace + (0ll * p.trace_cap + rec) * 4;
@@ -275,16 +278,21 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         }
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            // one K=64 step = 32 bytes along the swizzled 128-byte row = 2 address units
-                            constexpr bool nv = (SF_VEC == 16);
-                            const int sf_tile = nv ? j : (j >> 1);
-                            const int sf_id = nv ? 0 : 2 * (j & 1);
-                            const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
-                            mma_fp4_block_scaled<CTA_GROUP, SF_VEC>(
-                                d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
-                                tmem_base + Cfg::kTmemSfa + sf_tile * 4,
-                                tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4 + sfb_shift,
-                                (j > 0) ? 1u : accum0);
+                            // one MMA K step = 32 bytes along the swizzled 128-byte row = 2 address units
+                            if constexpr (Cfg::kDense) {
+                                mma_bf16<CTA_GROUP>(d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2),
+                                                    make_idesc_bf16(kMmaM, BLOCK_N), (j > 0) ? 1u : accum0);
+                            } else {
+                                constexpr bool nv = (SF_VEC == 16);
+                                const int sf_tile = nv ? j : (j >> 1);
+                                const int sf_id = nv ? 0 : 2 * (j & 1);
+                                const uint32_t idesc = make_idesc_fp4(kMmaM, BLOCK_N, kUe8m0, sf_id);
+                                mma_fp4_block_scaled<CTA_GROUP, (Cfg::kDense ? 16 : SF_VEC)>(
+                                    d_tmem, a_desc + static_cast<uint64_t>(j * 2), b_desc + static_cast<uint64_t>(j * 2), idesc,
+                                    tmem_base + Cfg::kTmemSfa + sf_tile * 4,
+                                    tmem_base + Cfg::kTmemSfb + sf_tile * Cfg::kNb * 4 + sfb_shift,
+                                    (j > 0) ? 1u : accum0);
+                            }
                         }
                         tcgen05_commit<CTA_GROUP>(bar_empty + stage * 8);
                         if (tr && rec < p.trace_cap) {

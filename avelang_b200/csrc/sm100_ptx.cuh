@@ -306,6 +306,31 @@ __device__ __forceinline__ void mma_fp4_block_scaled(uint32_t d_tmem, uint64_t a
     }
 }
 
+// Instruction descriptor for the dense bf16 MMA (kind::f16): bits 4-5 accumulator format (1 = fp32),
+// 7-9 A format (1 = bf16), 10-12 B format, 15/16 A/B major (0 = K-major), 17-22 N >> 3, 24-28 M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int mma_m, int mma_n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(mma_n >> 3) << 17) |
+           (static_cast<uint32_t>(mma_m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T for bf16 operands, K = 16 per instruction, fp32 accumulate.
+template <int CTA_GROUP>
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CTA_GROUP == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
 // Make `bar` (this CTA's barrier; with CTA_GROUP 2 the same offset in both CTAs of
 // the pair) receive one arrival when all tcgen05 operations issued so far by this
 // thread have completed.

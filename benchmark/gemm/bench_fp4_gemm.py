@@ -48,6 +48,8 @@ def run_fp4_gemm_benchmark(m, n, k, warmup, repeat, iters, validate, fmt="nvfp4"
     _ensure_b200()
     _validate_shape(m, n, k)
     dev = torch.device("cuda")
+    if fmt == "bf16":
+        return run_bf16_gemm_benchmark(m, n, k, warmup, repeat, iters, validate, seed, variant, use_graph)
     quant = ave.quantize_nvfp4 if fmt == "nvfp4" else ave.quantize_mxfp4
     gemm = ave.gemm_nvfp4_transposed_b if fmt == "nvfp4" else ave.gemm_mxfp4_transposed_b
     blk = 16 if fmt == "nvfp4" else 32
@@ -122,6 +124,52 @@ def run_fp4_gemm_benchmark(m, n, k, warmup, repeat, iters, validate, fmt="nvfp4"
     return elapsed
 
 
+def run_bf16_gemm_benchmark(m, n, k, warmup, repeat, iters, validate, seed=0, variant=0, use_graph=True):
+    """The reference operator on B200, measured exactly as benchmark/gemm/bench_amdgpu_gemm.py:23-68 does."""
+    from avelang_b200.bf16_gemm import gemm_pipeline_transposed_b
+
+    torch.manual_seed(seed)
+    A = torch.randn((m, k), dtype=torch.bfloat16, device="cuda")
+    B = torch.randn((n, k), dtype=torch.bfloat16, device="cuda")
+    C = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    for _ in range(warmup):
+        gemm_pipeline_transposed_b(A, B, out=C, variant=variant)
+    torch.cuda.synchronize()
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        capture_stream = torch.cuda.Stream()
+        with torch.cuda.graph(graph, stream=capture_stream):
+            gemm_pipeline_transposed_b(A, B, out=C, variant=variant)
+        torch.cuda.synchronize()
+        replay = graph.replay
+    else:
+        def replay():
+            gemm_pipeline_transposed_b(A, B, out=C, variant=variant)
+    start_evt = torch.cuda.Event(enable_timing=True)
+    end_evt = torch.cuda.Event(enable_timing=True)
+    start_evt.record()
+    for _ in range(repeat):
+        for _ in range(iters):
+            replay()
+    end_evt.record()
+    torch.cuda.synchronize()
+    ave.check_device_status(torch.device("cuda"))
+    elapsed = (start_evt.elapsed_time(end_evt) * 1.0e-3) / (repeat * iters)
+    flops = 2.0 * m * n * k
+    tflops = flops / elapsed / 1.0e12
+    bytes_moved = (m * k + k * n + m * n) * 2
+    bandwidth = bytes_moved / elapsed / 1.0e9
+    print(f"M={m} N={n} K={k} format=bf16 variant={variant} time_ms={elapsed * 1.0e3:.4f} tflops={tflops:.3f} bandwidth_gbs={bandwidth:.3f}")
+    if validate:
+        expected = (A.float().cpu() @ B.float().cpu().T).to(dtype=torch.bfloat16)
+        actual = C.to("cpu")
+        max_abs = torch.max(torch.abs(actual - expected)).item()
+        if not torch.allclose(actual, expected, rtol=1e-1, atol=1e-1):
+            raise AssertionError(f"Validation failed (max abs diff {max_abs}).")
+        print(f"validation=max_abs_diff:{max_abs:.6f}")
+    return elapsed
+
+
 def main():
     parser = argparse.ArgumentParser(description="Block-scaled FP4 GEMM benchmark (K multiple of 32, N multiple of 8)")
     parser.add_argument("--m", type=int, default=1024)
@@ -131,7 +179,7 @@ def main():
     parser.add_argument("--repeat", type=int, default=100)
     parser.add_argument("--iters", type=int, default=100, help="Graph replays per timing repeat")
     parser.add_argument("--validate", action="store_true", default=False)
-    parser.add_argument("--format", choices=["nvfp4", "mxfp4"], default="nvfp4")
+    parser.add_argument("--format", choices=["nvfp4", "mxfp4", "bf16"], default="nvfp4")
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--variant", type=int, default=0, help="kernel variant (0 = chosen by shape)")
     parser.add_argument("--rotate", type=int, default=1, help="operand sets cycled per pass (use >1 to defeat L2 reuse)")

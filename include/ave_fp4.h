@@ -145,6 +145,17 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The reference operator itself on sm_100a: D (m, n) bf16 = A (m, k) bf16 * B (n, k)^T bf16, fp32 accumulation in
+ * tensor memory (tcgen05.mma kind::f16), bf16 output rounded to nearest even (the reference's MI300 kernel
+ * truncates, python/avelang_kernels/amdgpu_gemm.py:322-328).  K % 8 == 0, ldd % 8 == 0, 16-byte aligned pointers;
+ * M and N need not be tile multiples (the reference requires M, N % 128 and K % 64, amdgpu_gemm.py:471-476).
+ * Stands in for the launch in gemm_pipeline_transposed_b, python/avelang_kernels/amdgpu_gemm.py:488-494.
+ * variant: AVE_FP4_GEMM_AUTO / AVE_FP4_GEMM_2CTA_N256 (256x256 tiles, CTA pairs) or AVE_FP4_GEMM_1CTA_N128.
+ */
+int ave_bf16_gemm(const void* a_bf16, const void* b_bf16, void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd,
+                  int variant, void* stream);
+
+/*
  * GEMM fused with the all-gather of its output (N-sharded weights on one NVLink/NVSwitch box).
  * As ave_fp4_gemm (tiled kernels, M > 64), and in addition every output tile is stored to
  * peer_d[0 .. n_peers-1]: device pointers, valid on THIS GPU, to the same (m, n) block inside each

@@ -22,7 +22,7 @@ def lib():
 def _declared_functions():
     text = open(os.path.join(ROOT, "include", "ave_fp4.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ave_fp4_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(ave_(?:fp4|bf16)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_symbols_are_exported(lib):
