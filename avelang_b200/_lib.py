@@ -20,7 +20,7 @@ _inited: set[int] = set()
 EXPORTS = (
     "ave_fp4_init", "ave_fp4_last_error", "ave_fp4_sf_bytes", "ave_fp4_workspace_bytes", "ave_fp4_amax",
     "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count", "ave_fp4_set_trace",
-    "ave_fp4_weight_tiles_bytes", "ave_fp4_pack_weight_tiles", "ave_fp4_gemm_decode_noalloc", "ave_fp4_gemm_allgather", "ave_fp4_quantize_nvfp4_dynamic", "ave_bf16_gemm",
+    "ave_fp4_weight_tiles_bytes", "ave_fp4_pack_weight_tiles", "ave_fp4_gemm_decode_noalloc", "ave_fp4_gemm_allgather", "ave_fp4_quantize_nvfp4_dynamic", "ave_bf16_gemm", "ave_fp4_selftest_wait_timeout",
 )
 
 
@@ -69,6 +69,8 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_quantize_nvfp4_dynamic.argtypes = [vp, i64, i64, i64, vp, vp, vp, i32, vp, vp]
         L.ave_bf16_gemm.restype = i32
         L.ave_bf16_gemm.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, vp]
+        L.ave_fp4_selftest_wait_timeout.restype = i32
+        L.ave_fp4_selftest_wait_timeout.argtypes = [i64, vp]
         L.ave_fp4_set_trace.restype = i32
         L.ave_fp4_set_trace.argtypes = [vp, i64]
         _lib = L

@@ -709,6 +709,17 @@ int ave_bf16_gemm(const void* a_bf16, const void* b_bf16, void* d_bf16, int64_t 
     }
 }
 
+int ave_fp4_selftest_wait_timeout(int64_t timeout_us, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (timeout_us < 1 || timeout_us > 100000)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_selftest_wait_timeout: timeout must be 1 us .. 100 ms, got %lld us", static_cast<long long>(timeout_us));
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ds->status, static_cast<unsigned long long>(timeout_us) * 1000ull);
+    AVE_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int ave_fp4_check(void* stream) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
@@ -719,7 +730,7 @@ int ave_fp4_check(void* stream) {
     AVE_CUDA(cudaMemcpy(&status, ds->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != 0) {
         AVE_CUDA(cudaMemset(ds->status, 0, sizeof(int)));
-        return fail(status, "ave-lang Error [CUDA]: a kernel gave up waiting (status %d: 101 producer, 102 MMA issuer, 103 epilogue)", status);
+        return fail(status, "ave-lang Error [CUDA]: a kernel gave up waiting (status %d: 101 producer, 102 MMA issuer, 103 epilogue, 104 self-test)", status);
     }
     return 0;
 }

@@ -30,7 +30,24 @@ enum GemmStatus : int {
     kStatusTimeoutProducer = 101,
     kStatusTimeoutMma = 102,
     kStatusTimeoutEpilogue = 103,
+    kStatusTimeoutSelfTest = 104,
 };
+
+// Exercises the failure path every kernel here relies on, without any fault: one warp waits on a
+// barrier that nobody will ever arrive on, the bounded wait gives up after `timeout_ns`, the kernel
+// records a status code and returns normally.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long timeout_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    if (!mbar_wait(b, 0, timeout_ns)) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusTimeoutSelfTest);
+    }
+}
 
 struct GemmParams {
     int m, n, k;

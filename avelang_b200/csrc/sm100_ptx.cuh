@@ -93,15 +93,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait.  Returns false when the phase did not complete within `timeout_ns`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long timeout_ns = kWaitTimeoutNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0xffu) == 0u) {
-            if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+            if (globaltimer_ns() - t0 > timeout_ns) return false;
         }
     }
 }

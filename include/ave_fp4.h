@@ -189,9 +189,16 @@ int ave_fp4_gemm_decode_noalloc(const void* a_packed, const void* a_scales, cons
  * Synchronises `stream`, reads and clears the device status word of the current
  * device.  Returns 0 if every kernel since the last check ran to completion, or the
  * positive status code a kernel recorded when one of its bounded waits expired
- * (101 producer, 102 MMA issuer, 103 epilogue).  Not capturable.
+ * (101 producer, 102 MMA issuer, 103 epilogue, 104 self-test).  Not capturable.
  */
 int ave_fp4_check(void* stream);
+
+/*
+ * Failure-path self-test: launches a one-warp kernel whose only barrier wait can never complete; the
+ * bounded wait expires after `timeout_us` (1 us .. 100 ms), the kernel records status 104 and returns
+ * normally.  The next ave_fp4_check then reports 104.  Nothing faults, traps or hangs.
+ */
+int ave_fp4_selftest_wait_timeout(int64_t timeout_us, void* stream);
 
 /*
  * Profiling aid (no counterpart in the reference, whose only tracing is event timing in
