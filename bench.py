@@ -168,6 +168,10 @@ def run_ours(args) -> dict:
     world, rank, local = dist_env()
     if world != args.gpus and world != 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    # default workload: every GPU runs the 8192-wide slice (weak scaling).  --workload c3: the prefill config,
+    # N = 57344 split over the ranks (strong scaling), same kernels.
+    c3 = (args.workload == "c3")
+    N = (57344 // world) if c3 else 8192
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the FP4 path has no CPU fallback")
     torch.cuda.set_device(local)
@@ -329,9 +333,11 @@ def run_ours(args) -> dict:
 
     out = {
         "metric": METRIC, "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+        "scaling": "strong" if c3 else "weak",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale, fp32 accumulate, bf16 out)", "data": "synthetic",
-        "config": {"workload": "c1_square_nvfp4_8192" if world == 1 else f"c1_per_gpu_slice_of_8192x{8192 * world}x8192_plus_allgather",
+        "config": {"workload": (f"c3_prefill_8192x57344x8192_nvfp4_n_sharded_x{world}" if c3 else
+                                "c1_square_nvfp4_8192" if world == 1 else f"c1_per_gpu_slice_of_8192x{8192 * world}x8192_plus_allgather"),
                    "m": M, "n_per_gpu": N, "k": K, "world": world,
                    "l2": f"{R} operand sets rotated; working set {R}x72 MB + 2x128 MB output > 126 MB L2",
                    "parallelism": (f"n-sharded x{world} + bf16 all-gather (" + ("fused peer stores" if fused else "nccl") + ")") if world > 1 else "single gpu"},
@@ -514,6 +520,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=512, help="rows of A in the CPU baseline sample")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--workload", default="c1", choices=["c1", "c3"],
+                    help="c1: 8192^3 per GPU (weak scaling, the headline); c3: 8192 x 57344 x 8192 with N split over the GPUs")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: exchange with NCCL after the GEMM instead of the fused epilogue")
     args = ap.parse_args()
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
