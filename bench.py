@@ -310,26 +310,71 @@ def run_ours(args) -> dict:
             clocks["sm_mhz_in_kernel"] = None
             clocks["sm_mhz_in_kernel_error"] = repr(exc)
 
-    # ---- end to end through the public operators with host buffers
-    host_d = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
-    a_dev = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
-    d_dev = outs[0]
+    # ---- end to end through the public operators with host buffers.  Every step copies its activations
+    # from pinned host memory, quantises, multiplies and copies the result back to pinned host memory.  On one
+    # GPU the three phases of consecutive steps run on three streams (double-buffered), so the PCIe link carries
+    # input and output at the same time; every step still does all of its copies inside the timed region.
+    e2e_steps = max(4, min(args.steps, 10))
+    if world == 1:
+        s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        a_buf = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        d_buf = outs
+        h_buf = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_comp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step(i: int):
-        a_dev.copy_(host_a[i % len(host_a)], non_blocking=True)
-        q = ave.quantize_nvfp4(a_dev)
-        if world > 1:
+        def e2e_step(i: int):
+            b = i % 2
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_comp[b])                 # the quantise that read a_buf[b] two steps ago is done
+                a_buf[b].copy_(host_a[i % len(host_a)], non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_comp):
+                s_comp.wait_event(ev_in[b])
+                s_comp.wait_event(ev_out[b])                # d_buf[b] has been copied out
+                q = ave.quantize_nvfp4(a_buf[b])
+                ave.gemm_nvfp4_transposed_b(q, B_ops[i % R], out=d_buf[b])
+                ev_comp[b].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[b])
+                h_buf[b].copy_(d_buf[b], non_blocking=True)
+                ev_out[b].record(s_out)
+
+        def timed_e2e(steps: int, warmup: int) -> float:
+            cur = torch.cuda.current_stream(dev)
+            for i in range(warmup):
+                e2e_step(i)
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cur)
+            for st in (s_in, s_comp, s_out):
+                st.wait_event(e0)
+            for i in range(steps):
+                e2e_step(i)
+            for st in (s_in, s_comp, s_out):
+                cur.wait_stream(st)
+            e1.record(cur)
+            torch.cuda.synchronize(dev)
+            return e0.elapsed_time(e1)
+
+        e2e_ms = timed_e2e(e2e_steps, 4) / e2e_steps
+        e2e_what = ("pinned host bf16 A -> device, amax + NVFP4 quantise, GEMM with resident pre-quantised B, bf16 D -> pinned host; "
+                    "copy-in, compute and copy-out of consecutive steps overlap on three streams")
+    else:
+        host_d = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+        a_dev = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+
+        def e2e_step(i: int):
+            a_dev.copy_(host_a[i % len(host_a)], non_blocking=True)
+            q = ave.quantize_nvfp4(a_dev)
             g = layers[i % R].forward(q)
             host_d.copy_(g[rank], non_blocking=True)
-        else:
-            ave.gemm_nvfp4_transposed_b(q, B_ops[i % R], out=d_dev)
-            host_d.copy_(d_dev, non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_ms = timed(e2e_step, e2e_steps, 3) / e2e_steps
+        e2e_ms = timed(e2e_step, e2e_steps, 3) / e2e_steps
+        e2e_what = "pinned host bf16 A -> device, amax + NVFP4 quantise, sharded GEMM + fused all-gather, this rank's bf16 slab -> pinned host"
     e2e = {"value": round(world * flops_per_gpu / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-           "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N, "ms_per_step": round(e2e_ms, 4),
-           "what": "pinned host bf16 A -> device, amax + NVFP4 quantise, GEMM with resident pre-quantised B, bf16 D -> pinned host"}
+           "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N, "ms_per_step": round(e2e_ms, 4), "what": e2e_what}
 
     out = {
         "metric": METRIC, "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
