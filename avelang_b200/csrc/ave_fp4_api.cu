@@ -324,8 +324,32 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
     if (variant == AVE_FP4_GEMM_SKINNY_TILED_W) return AVE_FP4_GEMM_SKINNY;
     if (variant != AVE_FP4_GEMM_AUTO) return variant;
     if (m <= 64) return AVE_FP4_GEMM_SKINNY;
-    (void)n;
-    return AVE_FP4_GEMM_2CTA_N256;
+    // Tiled kernels: estimate the time of each tile shape as (waves of tiles over the SMs) x (tile work) /
+    // (how well that shape feeds the tensor pipe, measured at 8192^3), and take the smallest.  Large problems
+    // get 256x256 CTA-pair tiles; problems with few tiles get smaller tiles so that more SMs have work.
+    struct Cand { int variant; int cta_m, bn, group; double eff; };
+    static const Cand cands[] = {
+        {AVE_FP4_GEMM_2CTA_N256, 256, 256, 2, 1.00},
+        {AVE_FP4_GEMM_2CTA_N128, 256, 128, 2, 0.87},
+        {AVE_FP4_GEMM_1CTA_N256, 128, 256, 1, 0.84},
+        {AVE_FP4_GEMM_1CTA_N128, 128, 128, 1, 0.76},
+    };
+    int sms = 148;
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
+    int best = AVE_FP4_GEMM_2CTA_N256;
+    double best_t = 0.0;
+    for (const Cand& c : cands) {
+        const double tiles = static_cast<double>((m + c.cta_m - 1) / c.cta_m) * static_cast<double>((n + c.bn - 1) / c.bn);
+        const double slots = static_cast<double>(sms / c.group);
+        const double waves = static_cast<double>(static_cast<long long>((tiles + slots - 1) / slots));
+        const double t = waves * (static_cast<double>(c.cta_m) * c.bn / c.group) / c.eff;   // per-SM work per wave
+        if (best_t == 0.0 || t < best_t) {
+            best_t = t;
+            best = c.variant;
+        }
+    }
+    return best;
 }
 
 // ------------------------------------------------------------------------------------

@@ -186,7 +186,17 @@ def pack_weight_tiles(op: Fp4Operand) -> Fp4Operand:
 
 def make_operand(packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor | None, fmt: int,
                  sf_layout: int = SF_ROW_MAJOR) -> Fp4Operand:
-    """Wrap tensors quantised elsewhere (e.g. offline weights) as an operand, checking shapes."""
+    """Wrap tensors quantised elsewhere (e.g. offline weights) as an operand, checking shapes.
+
+    torch's view-only dtypes are accepted and re-viewed as bytes: ``float4_e2m1fn_x2`` for the packed
+    values, ``float8_e4m3fn`` (NVFP4) / ``float8_e8m0fnu`` (MXFP4) for the scales.
+    """
+    f4 = getattr(torch, "float4_e2m1fn_x2", None)
+    if f4 is not None and packed.dtype == f4:
+        packed = packed.view(torch.uint8)
+    want_sf = getattr(torch, "float8_e4m3fn", None) if fmt == NVFP4 else getattr(torch, "float8_e8m0fnu", None)
+    if want_sf is not None and scales.dtype == want_sf:
+        scales = scales.view(torch.uint8)
     if packed.dtype != torch.uint8 or packed.dim() != 2:
         raise ValueError("packed must be a 2-D uint8 tensor (rows, K/2).")
     rows, k = packed.shape[0], packed.shape[1] * 2

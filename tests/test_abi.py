@@ -106,3 +106,16 @@ def test_inputs_are_deterministic():
     assert torch.isfinite(t.float()).all() and t.float().abs().max() > 4
     w = inputs.make_operand_bf16("weight", 64, 256, seed=2)
     assert 0.015 < w.float().std().item() < 0.025
+
+
+def test_make_operand_accepts_torch_fp4_fp8_views():
+    if not hasattr(torch, "float4_e2m1fn_x2") or not hasattr(torch, "float8_e8m0fnu"):
+        pytest.skip("this torch has no fp4 / e8m0 view dtypes")
+    packed = torch.arange(4 * 32, dtype=torch.uint8).reshape(4, 32)
+    sc_nv = torch.full((4, 4), 0x38, dtype=torch.uint8)
+    op = ave.make_operand(packed.view(torch.float4_e2m1fn_x2), sc_nv.view(torch.float8_e4m3fn), torch.ones(1), ave.NVFP4)
+    assert op.packed.dtype == torch.uint8 and op.scales.dtype == torch.uint8 and op.shape == (4, 64)
+    assert torch.equal(op.packed, packed)
+    sc_mx = torch.full((4, 2), 127, dtype=torch.uint8)
+    op = ave.make_operand(packed.view(torch.float4_e2m1fn_x2), sc_mx.view(torch.float8_e8m0fnu), None, ave.MXFP4)
+    assert op.scales.dtype == torch.uint8 and op.k == 64
