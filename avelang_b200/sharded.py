@@ -80,10 +80,19 @@ class ShardedFp4Linear:
         if self._gathered is not None and tuple(self._gathered.shape) == shape:
             return
         if self.fused:
-            import torch.distributed._symmetric_memory as symm
+            try:
+                import torch.distributed._symmetric_memory as symm
 
-            self._gathered = symm.empty(shape, dtype=torch.bfloat16, device=device)
-            self._hdl = symm.rendezvous(self._gathered, self.group if self.group is not None else dist.group.WORLD)
+                self._gathered = symm.empty(shape, dtype=torch.bfloat16, device=device)
+                self._hdl = symm.rendezvous(self._gathered, self.group if self.group is not None else dist.group.WORLD)
+            except Exception as exc:  # no peer-mapped memory on this system: exchange with NCCL after the GEMM instead
+                import warnings
+
+                warnings.warn(f"symmetric memory is unavailable ({exc!r}); ShardedFp4Linear uses the NCCL all-gather")
+                self.fused = False
+                self._hdl = None
+                self._gathered = torch.empty(shape, dtype=torch.bfloat16, device=device)
+                return
             slab_bytes = m * n_local * 2
             # this rank's slab inside every other rank's buffer; start with the next rank so that
             # the ranks do not all push to the same destination at once

@@ -272,7 +272,7 @@ def run_ours(args) -> dict:
         roofline["fused_step"] = {
             "target_ms": round(max(t_flop, t_link) * 1e3, 4), "achieved_ms": round(ms_per_step, 4),
             "frac": round(max(t_flop, t_link) * 1e3 / ms_per_step, 4), "bound": "nvlink" if t_link > t_flop else "tensor",
-            "exchange": "fused into the GEMM epilogue (peer stores) + device barrier" if fused else "NCCL all-gather after the GEMM",
+            "exchange": "fused into the GEMM epilogue (peer stores) + device barrier" if layers[0].fused else "NCCL all-gather after the GEMM",
             "gemm_only_ms": round(gemm_ms, 4), "nccl_allgather_only_ms": round(ag_ms, 4),
             "unfused_gemm_plus_nccl_ms": round(gemm_ms + ag_ms, 4),
             "gemm_only_tflops_per_gpu": round(gemm_tflops, 1),
