@@ -254,3 +254,50 @@ def test_static_weights_overlap_keeps_results(cuda_device, oracle):
     ave.check_device_status(cuda_device)
     for o, w in zip(outs, want):
         assert torch.equal(o, w)
+
+
+def test_mxfp4_16384_full_size(cuda_device, oracle):
+    """The MXFP4 config at full size (16384^3, Student-t activations, N(0, 0.02) weights): a row sample
+    against the oracle, quantise bytes of the sample bit-exact, and slab independence."""
+    m = n = k = 16384
+    a = inputs.student_t3_bf16(m, k, 0).to(cuda_device)
+    b = inputs.normal_bf16(n, k, 1, std=0.02).to(cuda_device)
+    A = ave.quantize_mxfp4(a, sf_layout=ave.SF_ROW_MAJOR)
+    B = ave.quantize_mxfp4(b, sf_layout=ave.SF_ROW_MAJOR)
+    d = ave.gemm_mxfp4_transposed_b(A, B)
+    ave.check_device_status(cuda_device)
+    rows = [0, 255, 256, 8191, 16383] + list(range(12000, 12011))
+    ridx = torch.tensor(rows, device=cuda_device)
+    ep, es, _ = oracle.c_quantize(_bits(a[ridx].cpu()), oracle.MXFP4)
+    assert np.array_equal(A.packed[ridx].cpu().numpy(), ep) and np.array_equal(A.scales[ridx].cpu().numpy(), es)
+    qa = (ep, es, 1.0)
+    qb = (B.packed.cpu().numpy(), B.scales.cpu().numpy(), 1.0)
+    _, dbf = oracle.c_gemm_fp4(qa, qb, oracle.MXFP4, want_f32=False)
+    _check(d[ridx], dbf, oracle, "16384^3 mxfp4 row sample")
+    slab = ave.Fp4Operand(A.packed[4096:4352], A.scales[4096:4352].contiguous(), None, A.fmt, 256, k, ave.SF_ROW_MAJOR)
+    assert torch.equal(ave.gemm_mxfp4_transposed_b(slab, B), d[4096:4352])
+
+
+def test_prefill_57344_full_size(cuda_device, oracle):
+    """The prefill config on one GPU (8192 x 57344 x 8192): a row sample against the oracle and the
+    N-shard property the multi-GPU path relies on -- each of 8 column shards computed on its own
+    (with the whole-tensor scale) equals the matching columns of the unsharded result."""
+    m, n, k = 8192, 57344, 8192
+    a = inputs.normal_bf16(m, k, 0).to(cuda_device)
+    A = ave.quantize_nvfp4(a, sf_layout=ave.SF_ROW_MAJOR)
+    del a
+    b = inputs.normal_bf16(n, k, 1).to(cuda_device)
+    B = ave.quantize_nvfp4(b, sf_layout=ave.SF_ROW_MAJOR)
+    del b
+    d = ave.gemm_nvfp4_transposed_b(A, B)
+    ave.check_device_status(cuda_device)
+    ridx = torch.tensor([0, 129, 4095, 8191], device=cuda_device)
+    qa = (A.packed[ridx].cpu().numpy(), A.scales[ridx].cpu().numpy(), float(A.global_scale.item()))
+    qb = (B.packed.cpu().numpy(), B.scales.cpu().numpy(), float(B.global_scale.item()))
+    _, dbf = oracle.c_gemm_fp4(qa, qb, oracle.NVFP4, want_f32=False)
+    _check(d[ridx], dbf, oracle, "prefill row sample")
+    per = n // 8
+    for r in (0, 3, 7):
+        shard = ave.Fp4Operand(B.packed[r * per:(r + 1) * per], B.scales[r * per:(r + 1) * per].contiguous(), B.global_scale,
+                               B.fmt, per, k, ave.SF_ROW_MAJOR)
+        assert torch.equal(ave.gemm_nvfp4_transposed_b(A, shard), d[:, r * per:(r + 1) * per])
