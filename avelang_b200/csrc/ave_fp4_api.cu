@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -118,6 +119,17 @@ int current_state(DeviceState** out) {
 
 // ----------------------------------------------------------------------------------
 // Tensor maps.
+// L2 fetch granularity of TMA loads (256 bytes unless AVE_FP4_L2_PROMOTION = 64 | 128 | 0 overrides it for tuning).
+CUtensorMapL2promotion l2_promotion() {
+    if (const char* e = getenv("AVE_FP4_L2_PROMOTION")) {
+        const int v = atoi(e);
+        if (v == 0) return CU_TENSOR_MAP_L2_PROMOTION_NONE;
+        if (v == 64) return CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
+        if (v == 128) return CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    }
+    return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
+
 int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
               uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
               const char* what) {
@@ -126,7 +138,7 @@ int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swz, l2_promotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(-AVE_FP4_ERR_ARG,
                     "tensor map for %s rejected (CUresult %d): base %p dims (%llu,%llu) stride %llu box (%u,%u)", what,
@@ -252,6 +264,17 @@ int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, i
     return 0;
 }
 
+// Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit);
+// AVE_FP4_SKINNY_BURST overrides it for tuning.
+int skinny_burst(int stages) {
+    int b = 4;
+    if (const char* e = getenv("AVE_FP4_SKINNY_BURST")) b = atoi(e);
+    const int cap = stages < 8 ? stages : 8;
+    if (b < 1) b = 1;
+    if (b > cap) b = cap;
+    return b;
+}
+
 int skinny_mp(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
 
 int64_t skinny_counter_bytes(int64_t n) {
@@ -292,6 +315,7 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.ldd = static_cast<int>(ldd);
     p.w_tile_major = w_tile_major ? 1 : 0;
     p.pdl = pdl ? 1 : 0;
+    p.burst = skinny_burst(ST);
     p.x_gs = xgs;
     p.w_gs = wgs;
     p.d = static_cast<__nv_bfloat16*>(d);

@@ -30,6 +30,7 @@ struct SkinnyParams {
     int ldd;              // row stride of D in elements
     int pdl;              // 1: launched with programmatic stream serialisation; weights may be read before the
                           //    previous kernel in the stream has finished, everything else waits for it
+    int burst;            // K blocks whose loads are issued together (1 .. min(8, STAGES))
     int w_tile_major;     // 0: W packed row-major (N, K/2); 1: 16 KB tiles [N/128][K/256][128 rows][128 B]
     const float* x_gs;    // device fp32 tensor scales or nullptr
     const float* w_gs;
@@ -143,8 +144,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             // Loads are issued in bursts of kBurst consecutive K blocks: the weight tiles of a
             // burst are neighbouring 128-byte pieces of the same 128 rows, so DRAM sees
             // 512 contiguous bytes per row and page visit instead of 128.
-            constexpr int kBurst = 4;
-            static_assert(kBurst <= STAGES, "burst must fit in the ring");
+            constexpr int kBurst = (STAGES < 8) ? STAGES : 8;   // upper bound; p.burst is the size used
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -156,7 +156,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             int left = static_cast<int>(u_end - u_begin);
             while (left > 0 && ok) {
                 const long long t0 = tr ? clock64() : 0;
-                const int g = left < kBurst ? left : kBurst;
+                const int g = left < p.burst ? left : p.burst;
                 // slots are released in order, so a free last slot means the whole burst is free
                 const int last = stage + g - 1;
                 const int last_stage = last >= STAGES ? last - STAGES : last;
