@@ -128,28 +128,44 @@ __device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ 
         const float u = fminf(gs_plain ? div_by_recip(t, gs, gs_recip) : __fdiv_rn(t, gs), 448.0f);
         code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
         const float d = __fmul_rn(e4m3_decode(code), gs);
-        const bool zero = (d == 0.0f);
-        const bool plain = divisor_is_plain(d);
-        const float rd = __frcp_rn(d);
+        // one of three paths per block, chosen outside the element loops: the common one (reciprocal
+        // division), all-zero block scale, and the rare divisors that need the plain division
+        if (d != 0.0f && divisor_is_plain(d)) {
+            const float rd = __frcp_rn(d);
 #pragma unroll
-        for (int w = 0; w < BLK / 8; ++w) {
-            float y[8];
+            for (int w = 0; w < BLK / 8; ++w) {
+                float y[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float lo = __uint_as_float(rw[w * 4 + i] << 16);
-                const float hi = __uint_as_float(rw[w * 4 + i] & 0xffff0000u);
-                if (zero) {
-                    y[2 * i] = copysignf(0.0f, lo);
-                    y[2 * i + 1] = copysignf(0.0f, hi);
-                } else if (plain) {
-                    y[2 * i] = div_by_recip(lo, d, rd);
-                    y[2 * i + 1] = div_by_recip(hi, d, rd);
-                } else {
-                    y[2 * i] = __fdiv_rn(lo, d);
-                    y[2 * i + 1] = __fdiv_rn(hi, d);
+                for (int i = 0; i < 4; ++i) {
+                    y[2 * i] = div_by_recip(__uint_as_float(rw[w * 4 + i] << 16), d, rd);
+                    y[2 * i + 1] = div_by_recip(__uint_as_float(rw[w * 4 + i] & 0xffff0000u), d, rd);
                 }
+                out_words[w] = pack8_e2m1(y);
             }
-            out_words[w] = pack8_e2m1(y);
+        } else if (d == 0.0f) {
+#pragma unroll
+            for (int w = 0; w < BLK / 8; ++w) {
+                // magnitudes are zero, each nibble keeps the sign bit of its element
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t v = rw[w * 4 + i];
+                    word |= ((v >> 15) & 1u) << (8 * i + 3);      // low half = even element
+                    word |= ((v >> 31) & 1u) << (8 * i + 7);      // high half = odd element
+                }
+                out_words[w] = word;
+            }
+        } else {
+#pragma unroll
+            for (int w = 0; w < BLK / 8; ++w) {
+                float y[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    y[2 * i] = __fdiv_rn(__uint_as_float(rw[w * 4 + i] << 16), d);
+                    y[2 * i + 1] = __fdiv_rn(__uint_as_float(rw[w * 4 + i] & 0xffff0000u), d);
+                }
+                out_words[w] = pack8_e2m1(y);
+            }
         }
     } else {
         if (a == 0.0f) {
