@@ -301,3 +301,24 @@ def test_prefill_57344_full_size(cuda_device, oracle):
         shard = ave.Fp4Operand(B.packed[r * per:(r + 1) * per], B.scales[r * per:(r + 1) * per].contiguous(), B.global_scale,
                                B.fmt, per, k, ave.SF_ROW_MAJOR)
         assert torch.equal(ave.gemm_nvfp4_transposed_b(A, shard), d[:, r * per:(r + 1) * per])
+
+
+def test_agrees_with_library_nvfp4_gemm(cuda_device):
+    """Independent cross-check of the storage conventions (nibble order, 128x4 scale tiles): torch's
+    `_scaled_mm` (the vendor library's NVFP4 GEMM) consumes the very same bytes.  It rounds to bf16 before
+    the tensor scales are applied, so the two results differ by one extra bf16 rounding (~2e-3)."""
+    if not hasattr(torch, "float4_e2m1fn_x2") or not hasattr(torch, "_scaled_mm"):
+        pytest.skip("this torch has no NVFP4 _scaled_mm")
+    m, n, k = 512, 768, 1024
+    A = ave.quantize_nvfp4(inputs.normal_bf16(m, k, 0).to(cuda_device))
+    B = ave.quantize_nvfp4(inputs.normal_bf16(n, k, 1).to(cuda_device))
+    ours = ave.gemm_nvfp4_transposed_b(A, B).float()
+    try:
+        lib = torch._scaled_mm(A.packed.view(torch.float4_e2m1fn_x2), B.packed.view(torch.float4_e2m1fn_x2).t(),
+                               scale_a=A.scales.view(torch.float8_e4m3fn), scale_b=B.scales.view(torch.float8_e4m3fn),
+                               out_dtype=torch.bfloat16)
+    except Exception as exc:  # library path not available for this build / shape
+        pytest.skip(f"library NVFP4 GEMM unavailable: {exc!r}"[:200])
+    ref = lib.float() * (A.global_scale * B.global_scale)
+    rel = (torch.linalg.norm(ours - ref) / torch.linalg.norm(ref)).item()
+    assert rel < 5e-3, rel
