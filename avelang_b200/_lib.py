@@ -12,6 +12,11 @@ import threading
 
 from . import build as _build
 
+class Epilogue(ctypes.Structure):
+    """struct ave_fp4_epilogue of include/ave_fp4.h."""
+    _fields_ = [("bias_bf16", ctypes.c_void_p), ("activation", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
 _lock = threading.Lock()
 _lib = None
 _inited: set[int] = set()
@@ -21,6 +26,7 @@ EXPORTS = (
     "ave_fp4_init", "ave_fp4_last_error", "ave_fp4_sf_bytes", "ave_fp4_workspace_bytes", "ave_fp4_amax",
     "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count", "ave_fp4_set_trace",
     "ave_fp4_weight_tiles_bytes", "ave_fp4_pack_weight_tiles", "ave_fp4_gemm_decode_noalloc", "ave_fp4_gemm_allgather", "ave_fp4_quantize_nvfp4_dynamic", "ave_bf16_gemm", "ave_fp4_selftest_wait_timeout",
+    "ave_fp4_gemm_epilogue",
 )
 
 
@@ -53,6 +59,8 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_sf_to_tiled.argtypes = [vp, i64, i64, vp, vp]
         L.ave_fp4_gemm.restype = i32
         L.ave_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, i64, vp]
+        L.ave_fp4_gemm_epilogue.restype = i32
+        L.ave_fp4_gemm_epilogue.argtypes = L.ave_fp4_gemm.argtypes + [ctypes.POINTER(Epilogue)]
         L.ave_fp4_check.restype = i32
         L.ave_fp4_check.argtypes = [vp]
         L.ave_fp4_sm_count.restype = i32

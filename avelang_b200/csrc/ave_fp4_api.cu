@@ -67,8 +67,14 @@ EncodeTiledFn g_encode = nullptr;
 template <int CG, int BN, int VEC, int ST, int ACC>
 cudaError_t prepare_gemm() {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
-    return cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if constexpr (VEC != 0) {   // the dense bf16 operator has no fused epilogue
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiBiasAct>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes);
+    }
+    return e;
 }
 
 template <int MP, int VEC, int ST>
@@ -170,7 +176,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 template <int CG, int BN, int VEC, int ST, int ACC>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
-                void* const* peers = nullptr, int n_peers = 0) {
+                void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
@@ -195,6 +201,8 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.status = ds.status;
     p.trace = ds.trace;
     p.trace_cap = ds.trace_cap;
+    p.bias = epi ? static_cast<const __nv_bfloat16*>(epi->bias_bf16) : nullptr;
+    p.act = epi ? epi->activation : 0;
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
@@ -213,7 +221,10 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+    if (p.bias != nullptr || p.act != 0)
+        AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiBiasAct>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+    else
+        AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
     return 0;
 }
 
@@ -289,7 +300,7 @@ int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
 template <int MP, int VEC, int ST>
 int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const float* xgs, const void* w, const void* sfw,
                   const float* wgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, void* workspace,
-                  bool w_tile_major, cudaStream_t stream, bool pdl = false) {
+                  bool w_tile_major, cudaStream_t stream, bool pdl = false, const ave_fp4_epilogue* epi = nullptr) {
     using Cfg = SkinnyConfig<MP, VEC, ST>;
     CUtensorMap tm_w, tm_x, tm_sfw, tm_sfx;
     int rc;
@@ -324,6 +335,8 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.status = ds.status;
     p.trace = ds.trace;
     p.trace_cap = ds.trace_cap;
+    p.bias = epi ? static_cast<const __nv_bfloat16*>(epi->bias_bf16) : nullptr;
+    p.act = epi ? epi->activation : 0;
 
     const long long units = static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
     long long grid = ds.sm_count;
@@ -647,7 +660,7 @@ int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k
 static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
                       const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                       int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
-                      void* const* peers, int n_peers) {
+                      void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
     if (rc) return rc;
@@ -660,13 +673,18 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
     if (!a_packed || !a_scales || !b_packed || !b_scales || !d_bf16 || !aligned16(a_packed) || !aligned16(a_scales) ||
         !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: null or misaligned (16-byte) pointer");
+    if (epi) {
+        if (epi->activation < AVE_FP4_ACT_NONE || epi->activation > AVE_FP4_ACT_SILU || epi->reserved != 0)
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: unknown activation %d (or reserved field not 0)", epi->activation);
+        if (epi->bias_bf16 && !aligned16(epi->bias_bf16)) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: bias must be 16-byte aligned");
+    }
     const float* ags = static_cast<const float*>(a_global_scale);
     const float* bgs = static_cast<const float*>(b_global_scale);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int v = resolve_variant(variant, m, n);
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
-#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi
     switch (v) {
         case AVE_FP4_GEMM_1CTA_N128:
             return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
@@ -686,7 +704,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
                 return fail(-AVE_FP4_ERR_WORKSPACE, "ave_fp4_gemm: workspace of %lld bytes (256-byte aligned, zero-initialised) required, got %lld",
                             static_cast<long long>(need), static_cast<long long>(workspace ? workspace_bytes : 0));
 #define SKINNY_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, \
-    (variant & ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) == AVE_FP4_GEMM_SKINNY_TILED_W, s, (variant & AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) != 0
+    (variant & ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) == AVE_FP4_GEMM_SKINNY_TILED_W, s, (variant & AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) != 0, epi
             const int mp = skinny_mp(m);
             if (mp == 16) return nv ? launch_skinny<16, 16, kStSkinny16>(SKINNY_ARGS) : launch_skinny<16, 32, kStSkinny16>(SKINNY_ARGS);
             if (mp == 32) return nv ? launch_skinny<32, 16, kStSkinny32>(SKINNY_ARGS) : launch_skinny<32, 32, kStSkinny32>(SKINNY_ARGS);
@@ -719,6 +737,14 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream) {
     return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
                       variant, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                          const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                          int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
+                          const ave_fp4_epilogue* epilogue) {
+    return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
+                      variant, workspace, workspace_bytes, stream, nullptr, 0, epilogue);
 }
 
 int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,

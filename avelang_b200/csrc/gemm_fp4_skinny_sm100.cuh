@@ -40,6 +40,8 @@ struct SkinnyParams {
     int* status;
     long long* trace;     // optional clock64() stamps of CTA 0 (same record layout as the tiled kernel)
     int trace_cap;
+    const __nv_bfloat16* bias;  // fused epilogue: n values (one per weight row), or nullptr
+    int act;                    // fused epilogue activation (Activation enum of the tiled kernel)
 };
 
 template <int MP, int SF_VEC, int STAGES>
@@ -306,6 +308,12 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         float alpha = 1.0f;
         if (p.x_gs) alpha *= __ldcg(p.x_gs);
         if (p.w_gs) alpha *= __ldcg(p.w_gs);
+        // tensor scales, then the optional fused bias (per weight row = output column) and activation
+        auto finish = [&](float acc, int col) -> float {
+            if (p.bias == nullptr && p.act == kActNone) return acc * alpha;
+            const float b = (p.bias != nullptr) ? __bfloat162float(p.bias[col]) : 0.0f;
+            return activate_rt(fmaf(acc, alpha, b), p.act);
+        };
         int seg = 0;
         bool ok = true;
         for (long long u = u_begin; u < u_end && ok; ++seg) {
@@ -342,7 +350,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 if (n < p.n) {
 #pragma unroll
                     for (int m = 0; m < MP; ++m)
-                        if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(__uint_as_float(v[m]) * alpha);
+                        if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(finish(__uint_as_float(v[m]), n));
                 }
             } else {
                 const int slot = (kb0 == 0) ? 1 : 0;
@@ -378,7 +386,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                     if (n < p.n) {
 #pragma unroll
                         for (int m = 0; m < MP; ++m)
-                            if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(sum[m] * alpha);
+                            if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(finish(sum[m], n));
                     }
                 }
             }

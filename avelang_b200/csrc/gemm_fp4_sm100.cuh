@@ -62,7 +62,50 @@ struct GemmParams {
     int* status;               // device status word, written on a wait timeout
     long long* trace;          // optional clock64() stamps of CTA 0 (profiling aid), or nullptr
     int trace_cap;             // records per role; record r of role q at trace[(q * trace_cap + r) * 4 ..+3]
+    const __nv_bfloat16* bias; // fused epilogue: n values added to every output row after the tensor scales, or nullptr
+    int act;                   // fused epilogue: kActNone / kActRelu / kActGelu / kActGeluTanh / kActSilu
 };
+
+// Activations of the fused epilogue, evaluated in fp32 on (scaled accumulator + bias) before the bf16 rounding.
+enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActGeluTanh = 3, kActSilu = 4 };
+
+template <int ACT>
+__device__ __forceinline__ float activate(float x) {
+    if constexpr (ACT == kActRelu) return fmaxf(x, 0.0f);
+    else if constexpr (ACT == kActGelu) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    else if constexpr (ACT == kActGeluTanh) return 0.5f * x * (1.0f + tanhf(0.79788456080286536f * (x + 0.044715f * x * x * x)));
+    else if constexpr (ACT == kActSilu) return x / (1.0f + expf(-x));
+    else return x;
+}
+
+__device__ __forceinline__ float activate_rt(float x, int act) {
+    switch (act) {
+        case kActRelu: return activate<kActRelu>(x);
+        case kActGelu: return activate<kActGelu>(x);
+        case kActGeluTanh: return activate<kActGeluTanh>(x);
+        case kActSilu: return activate<kActSilu>(x);
+        default: return x;
+    }
+}
+
+// fp32 accumulator columns (two per 32-bit word after the call) -> act(acc * alpha + bias[col]) as bf16 pairs.
+template <int ACT, int NCOLS>
+__device__ __forceinline__ void convert_bias_act(uint32_t (&packed)[NCOLS], float alpha, const __nv_bfloat16* bias, int col0, int n) {
+#pragma unroll
+    for (int i = 0; i < NCOLS / 2; ++i) {
+        float b0 = 0.0f, b1 = 0.0f;
+        const int col = col0 + 2 * i;
+        if (bias != nullptr && col < n) {
+            const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(bias + col));
+            b0 = __uint_as_float(w << 16);
+            b1 = __uint_as_float(w & 0xffff0000u);
+        }
+        const float lo = activate<ACT>(fmaf(__uint_as_float(packed[2 * i]), alpha, b0));
+        const float hi = activate<ACT>(fmaf(__uint_as_float(packed[2 * i + 1]), alpha, b1));
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+}
 
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
 struct GemmConfig {
@@ -120,7 +163,11 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
     tn = r / gm;
 }
 
-template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES>
+// EPI selects the epilogue at compile time, so that the plain kernel keeps its register allocation:
+// kEpiPlain: D = bf16(alpha * acc); kEpiBiasAct: D = bf16(act(alpha * acc + bias)).
+enum EpilogueKind : int { kEpiPlain = 0, kEpiBiasAct = 1 };
+
+template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(320, 1)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -366,12 +413,22 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 else mbar_arrive(bar_tempty + acc * 8);
             }
             // fp32 -> bf16 pairs in place: word i takes columns 2i and 2i+1
+            if constexpr (EPI == kEpiPlain) {
 #pragma unroll
-            for (int i = 0; i < Cfg::kEpiCols / 2; ++i) {
-                const float lo = __uint_as_float(packed[2 * i]) * alpha;
-                const float hi = __uint_as_float(packed[2 * i + 1]) * alpha;
-                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                for (int i = 0; i < Cfg::kEpiCols / 2; ++i) {
+                    const float lo = __uint_as_float(packed[2 * i]) * alpha;
+                    const float hi = __uint_as_float(packed[2 * i + 1]) * alpha;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            } else {
+                switch (p.act) {   // warp-uniform
+                    case kActRelu: convert_bias_act<kActRelu>(packed, alpha, p.bias, col0, p.n); break;
+                    case kActGelu: convert_bias_act<kActGelu>(packed, alpha, p.bias, col0, p.n); break;
+                    case kActGeluTanh: convert_bias_act<kActGeluTanh>(packed, alpha, p.bias, col0, p.n); break;
+                    case kActSilu: convert_bias_act<kActSilu>(packed, alpha, p.bias, col0, p.n); break;
+                    default: convert_bias_act<kActNone>(packed, alpha, p.bias, col0, p.n); break;
+                }
             }
             const long long te2 = tr ? clock64() : 0;
             // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so

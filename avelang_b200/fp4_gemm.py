@@ -225,9 +225,15 @@ def _workspace(L, device: torch.device, dev: int, m: int, n: int, k: int, fmt: i
     return ws
 
 
+ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
+
+
 def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int,
-          peer_ptrs: list[int] | None = None, static_weights: bool = False) -> torch.Tensor:
+          peer_ptrs: list[int] | None = None, static_weights: bool = False,
+          bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
     name = _FMT_NAME[fmt]
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(k for k in ACTIVATIONS if k)}, got {activation!r}.")
     if A.fmt != fmt:
         raise ValueError(f"A must be an {name} operand, got {_FMT_NAME.get(A.fmt, A.fmt)}.")
     if B.fmt != fmt:
@@ -256,6 +262,15 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         raise ValueError(f"out must be on device {A.device}, got {out.device}.")
     if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
         raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,):
+            raise ValueError(f"bias must be a bfloat16 tensor of shape ({n},), got {bias.dtype} {tuple(bias.shape)}.")
+        if bias.device != A.device:
+            raise ValueError(f"bias must be on device {A.device}, got {bias.device}.")
+        if not bias.is_contiguous() or bias.data_ptr() % 16 != 0:
+            raise ValueError("bias must be contiguous and 16-byte aligned.")
+        if peer_ptrs:
+            raise ValueError("the fused all-gather takes no bias or activation.")
     if m == 0 or n == 0:
         return out
     if A.tile_major:
@@ -285,6 +300,13 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         ws = _workspace(L, A.device, dev, m, n, k, fmt, variant)
         if static_weights:
             variant |= GEMM_FLAG_STATIC_WEIGHTS
+        if bias is not None or ACTIVATIONS[activation] != 0:
+            epi = _lib.Epilogue(None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], 0)
+            _lib.check(L.ave_fp4_gemm_epilogue(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed),
+                                               _ptr(B.scales), _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt,
+                                               variant, _ptr(ws), 0 if ws is None else ws.numel(), _stream(A.device),
+                                               ctypes.byref(epi)))
+            return out
         _lib.check(L.ave_fp4_gemm(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
                                   _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt, variant, _ptr(ws),
                                   0 if ws is None else ws.numel(), _stream(A.device)))
@@ -292,19 +314,23 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
 
 
 def gemm_nvfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
-                            variant: int = GEMM_AUTO, static_weights: bool = False) -> torch.Tensor:
+                            variant: int = GEMM_AUTO, static_weights: bool = False,
+                            bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
     """``out = A @ B.T`` for NVFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out.
 
     ``static_weights=True`` promises that B is not written by anything queued earlier on the stream; the
     decode kernel (M <= 64) then overlaps its start-up and first weight loads with the previous kernel.
+    ``bias`` ((N,) bf16) and ``activation`` ("relu", "gelu", "gelu_tanh", "silu") are fused into the epilogue:
+    ``out = act(A @ B.T + bias)``, evaluated in fp32 and rounded to bf16 once.
     """
-    return _gemm(A, B, out, NVFP4, variant, static_weights=static_weights)
+    return _gemm(A, B, out, NVFP4, variant, static_weights=static_weights, bias=bias, activation=activation)
 
 
 def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None = None,
-                            variant: int = GEMM_AUTO, static_weights: bool = False) -> torch.Tensor:
-    """``out = A @ B.T`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
-    return _gemm(A, B, out, MXFP4, variant, static_weights=static_weights)
+                            variant: int = GEMM_AUTO, static_weights: bool = False,
+                            bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
+    """``out = act(A @ B.T + bias)`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
+    return _gemm(A, B, out, MXFP4, variant, static_weights=static_weights, bias=bias, activation=activation)
 
 
 def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor, peer_ptrs: list[int],

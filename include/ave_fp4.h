@@ -145,6 +145,29 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
                  int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Fused epilogue of ave_fp4_gemm_epilogue: D = act(gsA * gsB * (A * B^T) + bias), evaluated in fp32 and
+ * rounded to bf16 once.  The reference operator has no epilogue (its write-out is
+ * python/avelang_kernels/amdgpu_gemm.py:293-329); this is the linear layer a caller builds around it.
+ */
+#define AVE_FP4_ACT_NONE 0
+#define AVE_FP4_ACT_RELU 1      /* max(x, 0) */
+#define AVE_FP4_ACT_GELU 2      /* 0.5 x (1 + erf(x / sqrt 2)) */
+#define AVE_FP4_ACT_GELU_TANH 3 /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) */
+#define AVE_FP4_ACT_SILU 4      /* x / (1 + exp(-x)) */
+
+typedef struct ave_fp4_epilogue {
+    const void* bias_bf16; /* device, n bf16 values, one per output column, 16-byte aligned; NULL = no bias */
+    int32_t activation;    /* AVE_FP4_ACT_* */
+    int32_t reserved;      /* must be 0 */
+} ave_fp4_epilogue;
+
+/* ave_fp4_gemm with the fused epilogue above (all kernel variants; epilogue == NULL is ave_fp4_gemm). */
+int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                          const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
+                          int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
+                          const ave_fp4_epilogue* epilogue);
+
+/*
  * The reference operator itself on sm_100a: D (m, n) bf16 = A (m, k) bf16 * B (n, k)^T bf16, fp32 accumulation in
  * tensor memory (tcgen05.mma kind::f16), bf16 output rounded to nearest even (the reference's MI300 kernel
  * truncates, python/avelang_kernels/amdgpu_gemm.py:322-328).  K % 8 == 0, ldd % 8 == 0, 16-byte aligned pointers;

@@ -294,3 +294,32 @@ int ave_oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/*
+ * Fused-epilogue restatement: y = act(d + bias[col]) on the fp32 GEMM result d (m, n), which already
+ * carries the tensor scales, evaluated in double and rounded to fp32, then to bf16 (RN-even) like the
+ * reference's oracle expression `.to(dtype=torch.bfloat16)` (test/examples/gemm/amdgpu/test_amdgpu_gemm.py:27).
+ * The reference has no epilogue; activation codes are those of include/ave_fp4.h
+ * (0 none, 1 relu, 2 gelu-erf, 3 gelu-tanh, 4 silu).  bias_bf16 may be NULL.
+ */
+void ave_oracle_bias_act(const float *d32, int64_t m, int64_t n, const uint16_t *bias_bf16, int act,
+                         float *y32, uint16_t *ybf16) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < m; ++i) {
+        for (int64_t j = 0; j < n; ++j) {
+            double x = (double)d32[i * n + j];
+            if (bias_bf16) x += (double)bits_to_f32((uint32_t)bias_bf16[j] << 16);
+            double y;
+            switch (act) {
+                case 1: y = x > 0.0 ? x : 0.0; break;
+                case 2: y = 0.5 * x * (1.0 + erf(x * 0.70710678118654752440)); break;
+                case 3: y = 0.5 * x * (1.0 + tanh(0.79788456080286535588 * (x + 0.044715 * x * x * x))); break;
+                case 4: y = x / (1.0 + exp(-x)); break;
+                default: y = x; break;
+            }
+            const float yf = (float)y;
+            if (y32) y32[i * n + j] = yf;
+            if (ybf16) ybf16[i * n + j] = ave_oracle_f32_to_bf16(yf);
+        }
+    }
+}

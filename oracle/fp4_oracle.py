@@ -76,6 +76,8 @@ def lib() -> ctypes.CDLL:
         L.ave_oracle_f32_to_bf16.argtypes = [f32]
         L.ave_oracle_num_threads.restype = i32
         L.ave_oracle_num_threads.argtypes = []
+        L.ave_oracle_bias_act.restype = None
+        L.ave_oracle_bias_act.argtypes = [vp, i64, i64, vp, i32, vp, vp]
         _lib = L
     return _lib
 
@@ -138,6 +140,43 @@ def c_gemm_fp4(a, b, fmt: int, want_f32: bool = True):
     if rc != 0:
         raise MemoryError("oracle temporaries")
     return d32, dbf
+
+
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+
+
+def c_bias_act(d32: np.ndarray, bias_bf16_bits: np.ndarray | None, act: int):
+    """Fused-epilogue restatement on the fp32 GEMM result: returns (y f32, y bf16 bits)."""
+    d32 = np.ascontiguousarray(d32, dtype=np.float32)
+    m, n = d32.shape
+    bias = None if bias_bf16_bits is None else np.ascontiguousarray(bias_bf16_bits, dtype=np.uint16)
+    if bias is not None and bias.shape != (n,):
+        raise ValueError("bias must have n entries")
+    y32 = np.empty_like(d32)
+    ybf = np.empty((m, n), dtype=np.uint16)
+    lib().ave_oracle_bias_act(_ptr(d32), m, n, None if bias is None else _ptr(bias), act, _ptr(y32), _ptr(ybf))
+    return y32, ybf
+
+
+def np_bias_act(d32: np.ndarray, bias_bf16_bits: np.ndarray | None, act: int):
+    """Independent numpy restatement of c_bias_act (double arithmetic, math.erf per element for GELU)."""
+    import math
+
+    x = d32.astype(np.float64)
+    if bias_bf16_bits is not None:
+        x = x + bf16_bits_to_f32(bias_bf16_bits).astype(np.float64)[None, :]
+    if act == ACT_RELU:
+        y = np.maximum(x, 0.0)
+    elif act == ACT_GELU:
+        y = 0.5 * x * (1.0 + np.vectorize(math.erf)(x / math.sqrt(2.0)))
+    elif act == ACT_GELU_TANH:
+        y = 0.5 * x * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+    elif act == ACT_SILU:
+        y = x / (1.0 + np.exp(-x))
+    else:
+        y = x
+    y32 = y.astype(np.float32)
+    return y32, f32_to_bf16_bits(y32)
 
 
 def c_sf_to_tiled(scales: np.ndarray) -> np.ndarray:

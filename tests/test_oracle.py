@@ -196,3 +196,22 @@ def test_bf16_rounding_is_nearest_even(oracle):
     want = torch.from_numpy(vals).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     assert np.array_equal(oracle.f32_to_bf16_bits(vals), want)
     assert [oracle.lib().ave_oracle_f32_to_bf16(np.float32(v)) for v in vals] == want.tolist()
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4])
+def test_bias_act_c_matches_numpy(oracle, act):
+    """The epilogue restatement: C (double libm) and numpy (math.erf / np.tanh / np.exp) agree to an fp32 ulp,
+    and known values hold."""
+    rng = np.random.default_rng(5)
+    d = (rng.standard_normal((37, 72)) * 3).astype(np.float32)
+    bias = oracle.f32_to_bf16_bits(rng.standard_normal(72).astype(np.float32))
+    y_c, b_c = oracle.c_bias_act(d, bias, act)
+    y_n, b_n = oracle.np_bias_act(d, bias, act)
+    assert np.allclose(y_c, y_n, rtol=3e-7, atol=1e-9)
+    # (1 + tanh(u)) cancels for very negative inputs, so results below 1e-6 may differ in their last digits
+    assert ((b_c != b_n) & (np.abs(y_c) > 1e-6)).mean() < 1e-3
+    one = np.array([[1.0, -1.0, 0.0]], dtype=np.float32)
+    expected = {0: [1.0, -1.0, 0.0], 1: [1.0, 0.0, 0.0], 2: [0.8413447, -0.15865526, 0.0],
+                3: [0.841192, -0.158808, 0.0], 4: [0.7310586, -0.26894143, 0.0]}[act]
+    y, _ = oracle.c_bias_act(one, None, act)
+    assert np.allclose(y[0], expected, rtol=1e-6, atol=1e-7)
