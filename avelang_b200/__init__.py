@@ -15,6 +15,7 @@ from .fp4_gemm import (  # noqa: F401
     check_device_status,
     gemm_mxfp4_transposed_b,
     gemm_nvfp4_transposed_b,
+    gemm_quantized_out_transposed_b,
     make_operand,
     pack_weight_tiles,
     quantize_mxfp4,
@@ -24,6 +25,6 @@ from .fp4_gemm import (  # noqa: F401
 
 __all__ = [
     "Fp4Operand", "quantize_nvfp4", "quantize_mxfp4", "gemm_nvfp4_transposed_b", "gemm_mxfp4_transposed_b",
-    "make_operand", "pack_weight_tiles", "to_tiled", "check_device_status", "NVFP4", "MXFP4", "SF_ROW_MAJOR", "SF_TILED",
+    "gemm_quantized_out_transposed_b", "make_operand", "pack_weight_tiles", "to_tiled", "check_device_status", "NVFP4", "MXFP4", "SF_ROW_MAJOR", "SF_TILED",
     "GEMM_AUTO", "GEMM_1CTA_N128", "GEMM_1CTA_N256", "GEMM_2CTA_N256", "GEMM_2CTA_N128", "GEMM_2CTA_N192", "GEMM_SKINNY",
 ]

@@ -14,7 +14,9 @@ from . import build as _build
 
 class Epilogue(ctypes.Structure):
     """struct ave_fp4_epilogue of include/ave_fp4.h."""
-    _fields_ = [("bias_bf16", ctypes.c_void_p), ("activation", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+    _fields_ = [("bias_bf16", ctypes.c_void_p), ("activation", ctypes.c_int32), ("quantize_out", ctypes.c_int32),
+                ("q_packed", ctypes.c_void_p), ("q_scales", ctypes.c_void_p), ("q_global_scale", ctypes.c_void_p),
+                ("q_sf_layout", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 _lock = threading.Lock()

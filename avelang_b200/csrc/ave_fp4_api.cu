@@ -73,6 +73,9 @@ cudaError_t prepare_gemm() {
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiBiasAct>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiQuant>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes);
     }
     return e;
 }
@@ -203,6 +206,11 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.trace_cap = ds.trace_cap;
     p.bias = epi ? static_cast<const __nv_bfloat16*>(epi->bias_bf16) : nullptr;
     p.act = epi ? epi->activation : 0;
+    const bool quant = epi && epi->quantize_out;
+    p.q_packed = quant ? static_cast<uint8_t*>(epi->q_packed) : nullptr;
+    p.q_sf = quant ? static_cast<uint8_t*>(epi->q_scales) : nullptr;
+    p.q_gs = quant ? static_cast<const float*>(epi->q_global_scale) : nullptr;
+    p.q_tiled = (quant && epi->q_sf_layout == AVE_FP4_SF_TILED) ? 1 : 0;
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
@@ -221,7 +229,9 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (p.bias != nullptr || p.act != 0)
+    if (quant)
+        AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiQuant>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+    else if (p.bias != nullptr || p.act != 0)
         AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiBiasAct>, tm_a, tm_b, tm_sfa, tm_sfb, p));
     else
         AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
@@ -670,18 +680,30 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
     if (m == 0 || n == 0) return 0;
     if (k == 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
     if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: ldd must be >= N and a multiple of 8, got %lld", static_cast<long long>(ldd));
-    if (!a_packed || !a_scales || !b_packed || !b_scales || !d_bf16 || !aligned16(a_packed) || !aligned16(a_scales) ||
+    const bool quant_out = epi && epi->quantize_out;
+    if (!a_packed || !a_scales || !b_packed || !b_scales || (!d_bf16 && !quant_out) || !aligned16(a_packed) || !aligned16(a_scales) ||
         !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: null or misaligned (16-byte) pointer");
     if (epi) {
         if (epi->activation < AVE_FP4_ACT_NONE || epi->activation > AVE_FP4_ACT_SILU || epi->reserved != 0)
             return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: unknown activation %d (or reserved field not 0)", epi->activation);
         if (epi->bias_bf16 && !aligned16(epi->bias_bf16)) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: bias must be 16-byte aligned");
+        if (quant_out) {
+            const int blk = (fmt == AVE_FP4_FMT_NVFP4) ? 16 : 32;
+            if (n % blk != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: a quantised result needs N %% %d == 0, got %lld", blk, static_cast<long long>(n));
+            if (!epi->q_packed || !epi->q_scales || !aligned16(epi->q_packed) || !aligned16(epi->q_scales))
+                return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: q_packed / q_scales null or misaligned (16-byte)");
+            if (fmt == AVE_FP4_FMT_NVFP4 && !epi->q_global_scale) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: NVFP4 result needs q_global_scale");
+            if (epi->q_sf_layout != AVE_FP4_SF_ROW_MAJOR && epi->q_sf_layout != AVE_FP4_SF_TILED)
+                return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: unknown q_sf_layout %d", epi->q_sf_layout);
+        }
     }
     const float* ags = static_cast<const float*>(a_global_scale);
     const float* bgs = static_cast<const float*>(b_global_scale);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int v = resolve_variant(variant, m, n);
+    int v = resolve_variant(variant, m, n);
+    if (quant_out && v == AVE_FP4_GEMM_SKINNY && (variant & ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) == AVE_FP4_GEMM_AUTO)
+        v = AVE_FP4_GEMM_1CTA_N128;   // the quantising epilogue lives in the tiled kernels
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
 #define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi
@@ -698,6 +720,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
             return nv ? launch_gemm<2, 192, 16, kSt2N192, 2>(GEMM_ARGS) : launch_gemm<2, 192, 32, kSt2N192, 2>(GEMM_ARGS);
         case AVE_FP4_GEMM_SKINNY: {
             if (n_peers > 0) return fail(-AVE_FP4_ERR_ARG, "the fused all-gather is served by the tiled kernels only (M > 64)");
+            if (epi && epi->quantize_out) return fail(-AVE_FP4_ERR_ARG, "the quantising epilogue is served by the tiled kernels only");
             if (m > 64) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: the skinny variant needs M <= 64, got %lld", static_cast<long long>(m));
             const int64_t need = skinny_workspace_bytes(m, n, ds->sm_count);
             if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))

@@ -21,6 +21,7 @@
 
 #include <cuda_bf16.h>
 
+#include "quantize_fp4.cuh"
 #include "sm100_ptx.cuh"
 
 namespace avefp4 {
@@ -64,6 +65,12 @@ struct GemmParams {
     int trace_cap;             // records per role; record r of role q at trace[(q * trace_cap + r) * 4 ..+3]
     const __nv_bfloat16* bias; // fused epilogue: n values added to every output row after the tensor scales, or nullptr
     int act;                   // fused epilogue: kActNone / kActRelu / kActGelu / kActGeluTanh / kActSilu
+    // quantising epilogue (kEpiQuant): the bf16-rounded result is also emitted as an FP4 operand of the
+    // kernel's own format, blocks along N, ready to be the A operand of the next GEMM
+    uint8_t* q_packed;         // (m, n/2) bytes, row-major
+    uint8_t* q_sf;             // scale bytes, layout q_tiled
+    const float* q_gs;         // NVFP4: device fp32 tensor scale of the result (static)
+    int q_tiled;               // 1: 128x4 tiled scale layout (padding written as zero), 0: row-major (m, n/blk)
 };
 
 // Activations of the fused epilogue, evaluated in fp32 on (scaled accumulator + bias) before the bf16 rounding.
@@ -165,7 +172,10 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
 
 // EPI selects the epilogue at compile time, so that the plain kernel keeps its register allocation:
 // kEpiPlain: D = bf16(alpha * acc); kEpiBiasAct: D = bf16(act(alpha * acc + bias)).
-enum EpilogueKind : int { kEpiPlain = 0, kEpiBiasAct = 1 };
+// kEpiQuant: kEpiBiasAct, then the bf16 values are quantised exactly as quantize_fp4_kernel would quantise them
+// (same device functions), so the packed nibbles and scale bytes equal those of the two-kernel sequence; the
+// bf16 matrix itself is written only if p.d is not null.
+enum EpilogueKind : int { kEpiPlain = 0, kEpiBiasAct = 1, kEpiQuant = 2 };
 
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(320, 1)
@@ -379,6 +389,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         float alpha = 1.0f;
         if (p.a_gs) alpha *= __ldg(p.a_gs);
         if (p.b_gs) alpha *= __ldg(p.b_gs);
+        // constants of the quantising epilogue (the divisions a / 6 / gs are done with reciprocals, see quantize_block)
+        float q_gs = 1.0f;
+        if (EPI == kEpiQuant && SF_VEC == 16 && p.q_gs != nullptr) q_gs = __ldg(p.q_gs);
+        const bool q_gs_plain = divisor_is_plain(q_gs);
+        const float q_gs_recip = __frcp_rn(q_gs);
+        const float sixth = __frcp_rn(6.0f);
         const uint32_t tempty0 = (CTA_GROUP == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
         const int my_groups = (half == 0) ? Cfg::kEpiGroups0 : Cfg::kEpiGroups1;   // warp-uniform
         const int my_col = (half == 0) ? 0 : Cfg::kEpiGroups0 * 64;
@@ -430,12 +446,54 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     default: convert_bias_act<kActNone>(packed, alpha, p.bias, col0, p.n); break;
                 }
             }
+            if constexpr (EPI == kEpiQuant && !Cfg::kDense) {
+                constexpr int QFMT = (SF_VEC == 16) ? kFmtNvfp4 : kFmtMxfp4;
+                constexpr int BLK = SF_VEC;                 // elements per scale block
+                constexpr int NB = 64 / BLK;                // blocks per 64-column group (4 or 2)
+                const int row = row0 + lane;
+                const int sf_cols = p.n / BLK;
+                const int k_atoms = (sf_cols + 3) / 4;
+                const int rows_pad = ((p.m + 127) / 128) * 128;
+#pragma unroll
+                for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
+                    if (g >= my_groups) break;
+                    const int colg = col0 + g * 64;
+                    uint32_t codes = 0;
+                    uint32_t w[8];
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        uint32_t code = quantize_block<QFMT>(&packed[g * 32 + b * (BLK / 2)], q_gs, q_gs_plain, q_gs_recip, sixth,
+                                                             &w[b * (BLK / 8)]);
+                        if (colg + b * BLK >= p.n || row >= p.m) code = 0;   // padding of the scale layout is zero
+                        codes |= code << (8 * b);
+                    }
+                    if (row < p.m) {
+                        uint8_t* dst = p.q_packed + static_cast<size_t>(row) * (p.n / 2) + colg / 2;
+#pragma unroll
+                        for (int h = 0; h < 4; ++h)     // 16 columns = 8 bytes each; N % 16 == 0
+                            if (colg + h * 16 < p.n) *reinterpret_cast<uint2*>(dst + h * 8) = make_uint2(w[2 * h], w[2 * h + 1]);
+                    }
+                    const int c = colg / BLK;           // first scale column of the group (multiple of NB)
+                    if (p.q_tiled) {
+                        if (row < rows_pad && c < k_atoms * 4) {
+                            uint8_t* sp = p.q_sf + sf_tiled_offset(row, c, k_atoms);
+                            if constexpr (NB == 4) *reinterpret_cast<uint32_t*>(sp) = codes;
+                            else *reinterpret_cast<uint16_t*>(sp) = static_cast<uint16_t>(codes);
+                        }
+                    } else if (row < p.m) {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (c + b < sf_cols) p.q_sf[static_cast<size_t>(row) * sf_cols + c + b] = static_cast<uint8_t>(codes >> (8 * b));
+                    }
+                }
+            }
             const long long te2 = tr ? clock64() : 0;
             // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so
             // that every global store instruction writes four complete 128-byte lines
 #pragma unroll
             for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
                 if (g >= my_groups) break;
+                if (EPI == kEpiQuant && p.d == nullptr) break;   // quantised result only
                 __syncwarp();
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {

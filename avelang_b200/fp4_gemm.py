@@ -230,7 +230,8 @@ ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu":
 
 def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, variant: int,
           peer_ptrs: list[int] | None = None, static_weights: bool = False,
-          bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
+          bias: torch.Tensor | None = None, activation: str | None = None,
+          quant: Fp4Operand | None = None, want_bf16: bool = True) -> torch.Tensor | None:
     name = _FMT_NAME[fmt]
     if activation not in ACTIVATIONS:
         raise ValueError(f"activation must be one of {sorted(k for k in ACTIVATIONS if k)}, got {activation!r}.")
@@ -252,7 +253,9 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
     if fmt == NVFP4 and (A.global_scale is None or B.global_scale is None):
         raise ValueError("NVFP4 operands need a global_scale tensor.")
     out_shape = (m, n)
-    if out is None:
+    if out is None and not want_bf16:
+        pass    # quantised result only
+    elif out is None:
         out = torch.empty(out_shape, dtype=torch.bfloat16, device=A.device)
     elif tuple(out.shape) != out_shape:
         raise ValueError(f"out must have shape {out_shape}, got {tuple(out.shape)}.")
@@ -260,7 +263,7 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         raise ValueError(f"out must have dtype torch.bfloat16, got {out.dtype}.")
     elif out.device != A.device:
         raise ValueError(f"out must be on device {A.device}, got {out.device}.")
-    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+    if out is not None and (out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0):
         raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
     if bias is not None:
         if bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,):
@@ -300,10 +303,17 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         ws = _workspace(L, A.device, dev, m, n, k, fmt, variant)
         if static_weights:
             variant |= GEMM_FLAG_STATIC_WEIGHTS
-        if bias is not None or ACTIVATIONS[activation] != 0:
+        if bias is not None or ACTIVATIONS[activation] != 0 or quant is not None:
             epi = _lib.Epilogue(None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], 0)
+            if quant is not None:
+                epi.quantize_out = 1
+                epi.q_packed = quant.packed.data_ptr()
+                epi.q_scales = quant.scales.data_ptr()
+                epi.q_global_scale = None if quant.global_scale is None else quant.global_scale.data_ptr()
+                epi.q_sf_layout = quant.sf_layout
+            ldd = n if out is None else out.stride(0)
             _lib.check(L.ave_fp4_gemm_epilogue(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed),
-                                               _ptr(B.scales), _ptr(B.global_scale), _ptr(out), m, n, k, out.stride(0), fmt,
+                                               _ptr(B.scales), _ptr(B.global_scale), _ptr(out), m, n, k, ldd, fmt,
                                                variant, _ptr(ws), 0 if ws is None else ws.numel(), _stream(A.device),
                                                ctypes.byref(epi)))
             return out
@@ -331,6 +341,43 @@ def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | No
                             bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
     """``out = act(A @ B.T + bias)`` for MXFP4 operands A (M, K) and B (N, K); fp32 accumulate, bf16 out."""
     return _gemm(A, B, out, MXFP4, variant, static_weights=static_weights, bias=bias, activation=activation)
+
+
+def gemm_quantized_out_transposed_b(A: Fp4Operand, B: Fp4Operand, out_global_scale: torch.Tensor | None = None,
+                                    bias: torch.Tensor | None = None, activation: str | None = None,
+                                    sf_layout: int = SF_TILED, out_bf16: torch.Tensor | bool | None = None,
+                                    variant: int = GEMM_AUTO) -> Fp4Operand | tuple[Fp4Operand, torch.Tensor]:
+    """``act(A @ B.T + bias)`` delivered as an FP4 operand (M, N) of A's format with its scale blocks along N --
+    the A operand of the next layer's GEMM -- straight from the GEMM epilogue, without the bf16 matrix going
+    through memory.  Bit-identical to quantising the bf16 result with ``quantize_nvfp4(out, global_scale=...)``
+    / ``quantize_mxfp4(out)``.  NVFP4 needs ``out_global_scale`` (a 1-element fp32 tensor: the static, calibrated
+    tensor scale of the result).  ``out_bf16``: True or a (M, N) bf16 tensor to receive the bf16 result as well;
+    then ``(operand, bf16)`` is returned."""
+    fmt = A.fmt
+    m, n = A.rows, B.rows
+    blk = 16 if fmt == NVFP4 else 32
+    if n % blk != 0:
+        raise ValueError(f"a quantised result needs N % {blk} == 0, got {n}.")
+    if fmt == NVFP4:
+        if out_global_scale is None or out_global_scale.dtype != torch.float32 or out_global_scale.numel() != 1:
+            raise ValueError("an NVFP4 result needs out_global_scale: a 1-element float32 tensor.")
+        if out_global_scale.device != A.device:
+            raise ValueError(f"out_global_scale must be on device {A.device}, got {out_global_scale.device}.")
+    else:
+        out_global_scale = None
+    if sf_layout not in (SF_ROW_MAJOR, SF_TILED):
+        raise ValueError(f"unknown sf_layout {sf_layout}.")
+    if variant in (GEMM_SKINNY, GEMM_SKINNY_TILED_W) or B.tile_major:
+        raise ValueError("the quantising epilogue is served by the tiled kernels only.")
+    packed = torch.empty((m, n // 2), dtype=torch.uint8, device=A.device)
+    scales = torch.empty((sf_bytes(m, n, fmt, sf_layout),), dtype=torch.uint8, device=A.device)
+    if sf_layout == SF_ROW_MAJOR:
+        scales = scales.view(m, n // blk)
+    q = Fp4Operand(packed, scales, out_global_scale, fmt, m, n, sf_layout)
+    want = out_bf16 is not None and out_bf16 is not False
+    res = _gemm(A, B, out_bf16 if isinstance(out_bf16, torch.Tensor) else None, fmt, variant, bias=bias,
+                activation=activation, quant=q, want_bf16=want)
+    return (q, res) if want else q
 
 
 def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor, peer_ptrs: list[int],

@@ -158,10 +158,23 @@ int ave_fp4_gemm(const void* a_packed, const void* a_scales, const void* a_globa
 typedef struct ave_fp4_epilogue {
     const void* bias_bf16; /* device, n bf16 values, one per output column, 16-byte aligned; NULL = no bias */
     int32_t activation;    /* AVE_FP4_ACT_* */
-    int32_t reserved;      /* must be 0 */
+    /*
+     * quantize_out != 0: the bf16-rounded result is also emitted as an FP4 operand of the GEMM's own format
+     * (`fmt`), scale blocks along N, i.e. ready to be the A operand of the next layer's GEMM -- bit-identical
+     * to running ave_fp4_quantize on the bf16 result (static tensor scale for NVFP4).  d_bf16 may then be NULL,
+     * in which case only the quantised result is written.  Needs n % 16 == 0 (NVFP4) or n % 32 == 0 (MXFP4) and
+     * a tiled kernel (AVE_FP4_GEMM_AUTO picks one for any M).
+     */
+    int32_t quantize_out;
+    void* q_packed;              /* (m, n/2) bytes, row-major, 16-byte aligned */
+    void* q_scales;              /* ave_fp4_sf_bytes(m, n, fmt, q_sf_layout) bytes */
+    const void* q_global_scale;  /* NVFP4: device fp32 tensor scale of the result (read, not written); MXFP4: unused */
+    int32_t q_sf_layout;         /* AVE_FP4_SF_ROW_MAJOR or AVE_FP4_SF_TILED */
+    int32_t reserved;            /* must be 0 */
 } ave_fp4_epilogue;
 
-/* ave_fp4_gemm with the fused epilogue above (all kernel variants; epilogue == NULL is ave_fp4_gemm). */
+/* ave_fp4_gemm with the fused epilogue above (bias and activation: all kernel variants; quantised result: the tiled
+ * kernels; epilogue == NULL is ave_fp4_gemm). */
 int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
                           const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                           int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
