@@ -76,13 +76,34 @@ struct GemmParams {
 // Activations of the fused epilogue, evaluated in fp32 on (scaled accumulator + bias) before the bf16 rounding.
 enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActGeluTanh = 3, kActSilu = 4 };
 
+// The epilogue warps have about 60 issue slots per element before they fall behind the tensor pipe, and a
+// call to a division or erff subroutine per element costs far more (silu with an IEEE division ran the 8192^3
+// GEMM at 2.5x its time).  So: sigmoid-type functions are x / (1 + e^-y) with ex2.approx and the approximate
+// division (a few ulp of fp32, far inside the bf16 rounding), and erf is Abramowitz & Stegun 7.1.26
+// (|error| < 1.5e-7), arranged so that negative inputs need no 1 + erf cancellation.
+__device__ __forceinline__ float sigmoid_mul(float x, float y) { return __fdividef(x, 1.0f + __expf(-y)); }   // x * sigmoid(y)
+
 template <int ACT>
 __device__ __forceinline__ float activate(float x) {
-    if constexpr (ACT == kActRelu) return fmaxf(x, 0.0f);
-    else if constexpr (ACT == kActGelu) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-    else if constexpr (ACT == kActGeluTanh) return 0.5f * x * (1.0f + tanhf(0.79788456080286536f * (x + 0.044715f * x * x * x)));
-    else if constexpr (ACT == kActSilu) return x / (1.0f + expf(-x));
-    else return x;
+    if constexpr (ACT == kActRelu) {
+        return fmaxf(x, 0.0f);
+    } else if constexpr (ACT == kActGelu) {
+        const float z = fabsf(x) * 0.70710678118654752f;
+        const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+        float poly = fmaf(1.061405429f, t, -1.453152027f);
+        poly = fmaf(poly, t, 1.421413741f);
+        poly = fmaf(poly, t, -0.284496736f);
+        poly = fmaf(poly, t, 0.254829592f);
+        const float e = poly * t * __expf(-z * z);          // erfc(z), z >= 0
+        return (x >= 0.0f) ? x * fmaf(-0.5f, e, 1.0f) : 0.5f * x * e;
+    } else if constexpr (ACT == kActGeluTanh) {
+        // 0.5 (1 + tanh u) = sigmoid(2u)
+        return sigmoid_mul(x, 1.59576912160573071f * (x + 0.044715f * x * x * x));
+    } else if constexpr (ACT == kActSilu) {
+        return sigmoid_mul(x, x);
+    } else {
+        return x;
+    }
 }
 
 __device__ __forceinline__ float activate_rt(float x, int act) {
