@@ -28,7 +28,7 @@ EXPORTS = (
     "ave_fp4_init", "ave_fp4_last_error", "ave_fp4_sf_bytes", "ave_fp4_workspace_bytes", "ave_fp4_amax",
     "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count", "ave_fp4_set_trace",
     "ave_fp4_weight_tiles_bytes", "ave_fp4_pack_weight_tiles", "ave_fp4_gemm_decode_noalloc", "ave_fp4_gemm_allgather", "ave_fp4_quantize_nvfp4_dynamic", "ave_bf16_gemm", "ave_fp4_selftest_wait_timeout",
-    "ave_fp4_gemm_epilogue",
+    "ave_fp4_gemm_epilogue", "ave_fp4_gemm_partials", "ave_fp4_reduce_partials",
 )
 
 
@@ -63,6 +63,10 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, i64, vp]
         L.ave_fp4_gemm_epilogue.restype = i32
         L.ave_fp4_gemm_epilogue.argtypes = L.ave_fp4_gemm.argtypes + [ctypes.POINTER(Epilogue)]
+        L.ave_fp4_gemm_partials.restype = i32
+        L.ave_fp4_gemm_partials.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i32, vp]
+        L.ave_fp4_reduce_partials.restype = i32
+        L.ave_fp4_reduce_partials.argtypes = [vp, i32, i64, i64, vp, i64, ctypes.POINTER(Epilogue), vp]
         L.ave_fp4_check.restype = i32
         L.ave_fp4_check.argtypes = [vp]
         L.ave_fp4_sm_count.restype = i32

@@ -76,6 +76,9 @@ cudaError_t prepare_gemm() {
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiQuant>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::kSmemBytes);
+        if (e == cudaSuccess && CG == 2 && BN == 256)   // K-sharded partial results: the 256x256 CTA-pair tile only
+            e = cudaFuncSetAttribute(gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiPartial>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes);
     }
     return e;
 }
@@ -179,7 +182,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 template <int CG, int BN, int VEC, int ST, int ACC>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
-                void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr) {
+                void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr,
+                void* const* slabs = nullptr, int rs_world = 0) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
@@ -211,6 +215,9 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.q_sf = quant ? static_cast<uint8_t*>(epi->q_scales) : nullptr;
     p.q_gs = quant ? static_cast<const float*>(epi->q_global_scale) : nullptr;
     p.q_tiled = (quant && epi->q_sf_layout == AVE_FP4_SF_TILED) ? 1 : 0;
+    p.rs_world = rs_world;
+    p.rs_rows = rs_world > 0 ? static_cast<int>(m / rs_world) : 0;
+    for (int i = 0; i < 8; ++i) p.rs_dst[i] = (i < rs_world) ? static_cast<float*>(slabs[i]) : nullptr;
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
@@ -229,7 +236,12 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (quant)
+    if (rs_world > 0) {
+        if constexpr (CG == 2 && BN == 256)
+            AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiPartial>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+        else
+            return fail(-AVE_FP4_ERR_ARG, "partial results are served by the 256x256 CTA-pair kernel only");
+    } else if (quant)
         AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiQuant>, tm_a, tm_b, tm_sfa, tm_sfb, p));
     else if (p.bias != nullptr || p.act != 0)
         AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiBiasAct>, tm_a, tm_b, tm_sfa, tm_sfb, p));
@@ -670,7 +682,8 @@ int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k
 static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
                       const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                       int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
-                      void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr) {
+                      void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr, void* const* slabs = nullptr,
+                      int rs_world = 0) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
     if (rc) return rc;
@@ -681,7 +694,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
     if (k == 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
     if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: ldd must be >= N and a multiple of 8, got %lld", static_cast<long long>(ldd));
     const bool quant_out = epi && epi->quantize_out;
-    if (!a_packed || !a_scales || !b_packed || !b_scales || (!d_bf16 && !quant_out) || !aligned16(a_packed) || !aligned16(a_scales) ||
+    if (!a_packed || !a_scales || !b_packed || !b_scales || (!d_bf16 && !quant_out && rs_world == 0) || !aligned16(a_packed) || !aligned16(a_scales) ||
         !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: null or misaligned (16-byte) pointer");
     if (epi) {
@@ -706,7 +719,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
         v = AVE_FP4_GEMM_1CTA_N128;   // the quantising epilogue lives in the tiled kernels
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
-#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi, slabs, rs_world
     switch (v) {
         case AVE_FP4_GEMM_1CTA_N128:
             return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
@@ -768,6 +781,49 @@ int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void
                           const ave_fp4_epilogue* epilogue) {
     return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
                       variant, workspace, workspace_bytes, stream, nullptr, 0, epilogue);
+}
+
+int ave_fp4_gemm_partials(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int64_t m,
+                          int64_t n, int64_t k, int fmt, void* stream) {
+    if (world < 1 || world > 8) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: world must be 1..8, got %d", world);
+    if (slab_dst == nullptr) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: slab_dst is NULL");
+    if (m <= 0 || m % (static_cast<int64_t>(world) * 32) != 0)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: M must be a positive multiple of 32 * world, got %lld", static_cast<long long>(m));
+    for (int i = 0; i < world; ++i)
+        if (!slab_dst[i] || !aligned16(slab_dst[i])) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: slab pointer %d is null or misaligned", i);
+    return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, nullptr, m, n, k, n, fmt,
+                      AVE_FP4_GEMM_2CTA_N256, nullptr, 0, stream, nullptr, 0, nullptr, slab_dst, world);
+}
+
+int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int64_t n, void* d_bf16, int64_t ldd,
+                            const ave_fp4_epilogue* epilogue, void* stream) {
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (world < 1 || world > 8) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_reduce_partials: world must be 1..8, got %d", world);
+    if (rows < 0 || n < 0 || n % 8 != 0 || ldd < n || ldd % 8 != 0)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_reduce_partials: N and ldd must be multiples of 8 and ldd >= N");
+    if (rows == 0 || n == 0) return 0;
+    if (!slabs_f32 || !d_bf16 || !aligned16(slabs_f32) || !aligned16(d_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_reduce_partials: null or misaligned (16-byte) pointer");
+    const __nv_bfloat16* bias = nullptr;
+    int act = 0;
+    if (epilogue) {
+        if (epilogue->activation < AVE_FP4_ACT_NONE || epilogue->activation > AVE_FP4_ACT_SILU || epilogue->reserved != 0 || epilogue->quantize_out)
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_reduce_partials: epilogue takes a bias and an activation only");
+        if (epilogue->bias_bf16 && !aligned16(epilogue->bias_bf16)) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_reduce_partials: bias must be 16-byte aligned");
+        bias = static_cast<const __nv_bfloat16*>(epilogue->bias_bf16);
+        act = epilogue->activation;
+    }
+    const long long groups = rows * (n / 8);
+    long long blocks = (groups + 255) / 256;
+    const long long cap = static_cast<long long>(ds->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    reduce_partials_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float*>(slabs_f32), world, rows, n, static_cast<__nv_bfloat16*>(d_bf16), ldd, bias, act);
+    AVE_CUDA(cudaGetLastError());
+    return 0;
 }
 
 int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,

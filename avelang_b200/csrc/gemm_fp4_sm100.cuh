@@ -71,6 +71,11 @@ struct GemmParams {
     uint8_t* q_sf;             // scale bytes, layout q_tiled
     const float* q_gs;         // NVFP4: device fp32 tensor scale of the result (static)
     int q_tiled;               // 1: 128x4 tiled scale layout (padding written as zero), 0: row-major (m, n/blk)
+    // fp32 partial result for a K-sharded GEMM (kEpiPartial): rows [j * rs_rows, (j + 1) * rs_rows) go, row stride n,
+    // to rs_dst[j] -- the slab this rank owns inside rank j's staging buffer (peer-mapped for j != this rank)
+    float* rs_dst[8];
+    int rs_rows;               // rows per owner, a multiple of 32
+    int rs_world;
 };
 
 // Activations of the fused epilogue, evaluated in fp32 on (scaled accumulator + bias) before the bf16 rounding.
@@ -196,7 +201,9 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
 // kEpiQuant: kEpiBiasAct, then the bf16 values are quantised exactly as quantize_fp4_kernel would quantise them
 // (same device functions), so the packed nibbles and scale bytes equal those of the two-kernel sequence; the
 // bf16 matrix itself is written only if p.d is not null.
-enum EpilogueKind : int { kEpiPlain = 0, kEpiBiasAct = 1, kEpiQuant = 2 };
+// kEpiPartial: alpha * acc is written as fp32 (no rounding) to the slab of the rank that owns the row: the
+// first half of a K-sharded GEMM + reduce-scatter, with the scatter done by the epilogue's own (peer) stores.
+enum EpilogueKind : int { kEpiPlain = 0, kEpiBiasAct = 1, kEpiQuant = 2, kEpiPartial = 3 };
 
 template <int CTA_GROUP, int BLOCK_N, int SF_VEC, int STAGES, int ACC_STAGES, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(320, 1)
@@ -450,7 +457,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 else mbar_arrive(bar_tempty + acc * 8);
             }
             // fp32 -> bf16 pairs in place: word i takes columns 2i and 2i+1
-            if constexpr (EPI == kEpiPlain) {
+            if constexpr (EPI == kEpiPartial) {
+#pragma unroll
+                for (int i = 0; i < Cfg::kEpiCols; ++i) packed[i] = __float_as_uint(__uint_as_float(packed[i]) * alpha);
+            } else if constexpr (EPI == kEpiPlain) {
 #pragma unroll
                 for (int i = 0; i < Cfg::kEpiCols / 2; ++i) {
                     const float lo = __uint_as_float(packed[2 * i]) * alpha;
@@ -511,9 +521,19 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const long long te2 = tr ? clock64() : 0;
             // ---- write out: 32 rows x 64 columns at a time through a swizzled transpose, so
             // that every global store instruction writes four complete 128-byte lines
+            // A 128-byte row piece is 64 bf16 columns, or 32 fp32 columns of a partial result.
+            constexpr int kPieceCols = (EPI == kEpiPartial) ? 32 : 64;
+            constexpr int kPieces0 = Cfg::kEpiCols / kPieceCols;
+            const int my_pieces = my_groups * (64 / kPieceCols);
+            // partial results: all 32 rows of this warp belong to one owner (rs_rows is a multiple of 32)
+            float* rs_base = nullptr;
+            if constexpr (EPI == kEpiPartial) {
+                const int owner = min(row0 / p.rs_rows, p.rs_world - 1);
+                rs_base = p.rs_dst[owner] - static_cast<size_t>(owner) * p.rs_rows * p.n;
+            }
 #pragma unroll
-            for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
-                if (g >= my_groups) break;
+            for (int g = 0; g < kPieces0; ++g) {
+                if (g >= my_pieces) break;
                 if (EPI == kEpiQuant && p.d == nullptr) break;   // quantised result only
                 __syncwarp();
 #pragma unroll
@@ -527,7 +547,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
                 __syncwarp();
                 const int q = lane & 7;
-                const int col = col0 + g * 64 + q * 8;
+                const int col = col0 + g * kPieceCols + q * (kPieceCols / 8);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int r = i * 4 + (lane >> 3);
@@ -536,14 +556,18 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr) : "memory");
                     const int row = row0 + r;
                     if (row < p.m && col < p.n) {
-                        // streaming store: the output is not re-read here and should not push the
-                        // operands (which other CTAs still need) out of L2
-                        const size_t off = static_cast<size_t>(row) * p.ldd + col;
-                        __stcs(reinterpret_cast<uint4*>(p.d + off), make_uint4(w0, w1, w2, w3));
-                        // fused all-gather: push the same 128-byte lines straight into every peer's copy
-                        // over NVLink (plain peer stores), so the exchange overlaps the next tiles' math
-                        for (int pi = 0; pi < p.n_peers; ++pi)
-                            __stcs(reinterpret_cast<uint4*>(p.peer_d[pi] + off), make_uint4(w0, w1, w2, w3));
+                        if constexpr (EPI == kEpiPartial) {
+                            __stcs(reinterpret_cast<uint4*>(rs_base + static_cast<size_t>(row) * p.n + col), make_uint4(w0, w1, w2, w3));
+                        } else {
+                            // streaming store: the output is not re-read here and should not push the
+                            // operands (which other CTAs still need) out of L2
+                            const size_t off = static_cast<size_t>(row) * p.ldd + col;
+                            __stcs(reinterpret_cast<uint4*>(p.d + off), make_uint4(w0, w1, w2, w3));
+                            // fused all-gather: push the same 128-byte lines straight into every peer's copy
+                            // over NVLink (plain peer stores), so the exchange overlaps the next tiles' math
+                            for (int pi = 0; pi < p.n_peers; ++pi)
+                                __stcs(reinterpret_cast<uint4*>(p.peer_d[pi] + off), make_uint4(w0, w1, w2, w3));
+                        }
                     }
                 }
             }
@@ -558,6 +582,47 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     __syncthreads();
     if constexpr (CTA_GROUP == 2) cluster_sync_all();
     if (warp == 1) tmem_dealloc<CTA_GROUP>(tmem_base, Cfg::kTmemCols);
+}
+
+// Second half of the K-sharded GEMM + reduce-scatter: D (rows, n) bf16 = act(sum over r of slab r + bias), slabs
+// fp32 (rows, n) back to back, summed in slab order so that the result does not depend on arrival order.
+// A thread takes 8 consecutive columns: two 128-bit loads per slab, one 128-bit store.
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ slabs, int world, long long rows, long long n, __nv_bfloat16* __restrict__ d,
+                       long long ldd, const __nv_bfloat16* __restrict__ bias, int act) {
+    const long long groups_per_row = n / 8;
+    const long long total = rows * groups_per_row;
+    const long long slab_elems = rows * n;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < total;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = g / groups_per_row;
+        const long long c = (g - r * groups_per_row) * 8;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int w = 0; w < world; ++w) {
+            const float4* src = reinterpret_cast<const float4*>(slabs + w * slab_elems + r * n + c);
+            const float4 lo = __ldcs(src), hi = __ldcs(src + 1);
+            acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+            acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+        }
+        if (bias != nullptr) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + c));
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __uint_as_float(bw[i] << 16);
+                acc[2 * i + 1] += __uint_as_float(bw[i] & 0xffff0000u);
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(activate_rt(acc[2 * i], act), activate_rt(acc[2 * i + 1], act));
+            o[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(d + r * ldd + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 }  // namespace avefp4

@@ -387,6 +387,68 @@ def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor,
     return _gemm(A, B, out, A.fmt, variant, peer_ptrs)
 
 
+def gemm_partials_transposed_b(A: Fp4Operand, B: Fp4Operand, slab_ptrs: list[int]) -> None:
+    """First half of a K-sharded GEMM + reduce-scatter.  A (M, K_r) and B (N, K_r) are this rank's K-slices; the
+    fp32 product is scattered by rows: rows ``[j*M/w, (j+1)*M/w)`` are stored (row stride N) at ``slab_ptrs[j]``,
+    raw device addresses valid on this GPU (peer-mapped for other ranks' buffers), ``w = len(slab_ptrs)``."""
+    fmt = A.fmt
+    if B.fmt != fmt:
+        raise ValueError("A and B must have the same format.")
+    m, k, n = A.rows, A.k, B.rows
+    world = len(slab_ptrs)
+    if B.k != k:
+        raise ValueError(f"A and B must share K, got {k} and {B.k}.")
+    if not 1 <= world <= 8:
+        raise ValueError(f"1..8 slabs, got {world}.")
+    if m <= 0 or m % (32 * world) != 0:
+        raise ValueError(f"M must be a positive multiple of 32 * world = {32 * world}, got {m}.")
+    if n % 8 != 0 or k % 32 != 0 or k == 0:
+        raise ValueError(f"N must be a multiple of 8 and K a positive multiple of 32, got N = {n}, K = {k}.")
+    if A.tile_major or B.tile_major:
+        raise ValueError("tile-major operands serve the decode kernel only.")
+    if fmt == NVFP4 and (A.global_scale is None or B.global_scale is None):
+        raise ValueError("NVFP4 operands need a global_scale tensor.")
+    dev = _require_cuda(A.packed, "A")
+    if B.device != A.device:
+        raise ValueError(f"B must be on device {A.device}, got {B.device}.")
+    A = to_tiled(A)
+    B = to_tiled(B)
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        arr = (ctypes.c_void_p * world)(*slab_ptrs)
+        _lib.check(L.ave_fp4_gemm_partials(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
+                                           _ptr(B.global_scale), arr, world, m, n, k, fmt, _stream(A.device)))
+
+
+def reduce_partials(slabs: torch.Tensor, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                    activation: str | None = None) -> torch.Tensor:
+    """Second half: ``out (rows, N) bf16 = act(slabs.sum(0) + bias)`` for fp32 slabs (world, rows, N), summed in slab
+    order, rounded once."""
+    if slabs.dtype != torch.float32 or slabs.dim() != 3 or not slabs.is_contiguous():
+        raise ValueError("slabs must be a contiguous float32 tensor (world, rows, N).")
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(k for k in ACTIVATIONS if k)}, got {activation!r}.")
+    world, rows, n = slabs.shape
+    dev = _require_cuda(slabs, "slabs")
+    if n % 8 != 0:
+        raise ValueError(f"N must be a multiple of 8, got {n}.")
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=slabs.device)
+    elif tuple(out.shape) != (rows, n) or out.dtype != torch.bfloat16 or out.device != slabs.device:
+        raise ValueError(f"out must be a bfloat16 tensor of shape {(rows, n)} on {slabs.device}.")
+    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
+    if bias is not None and (bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,) or bias.device != slabs.device
+                             or not bias.is_contiguous() or bias.data_ptr() % 16 != 0):
+        raise ValueError(f"bias must be a contiguous, 16-byte aligned bfloat16 tensor of shape ({n},) on {slabs.device}.")
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        epi = _lib.Epilogue(None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], 0)
+        _lib.check(L.ave_fp4_reduce_partials(_ptr(slabs), world, rows, n, _ptr(out), out.stride(0), ctypes.byref(epi),
+                                             _stream(slabs.device)))
+    return out
+
+
 def check_device_status(device: torch.device | None = None) -> None:
     """Synchronise the current stream and raise if a kernel recorded a wait time-out."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device

@@ -14,7 +14,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from .fp4_gemm import Fp4Operand, gemm_allgather_transposed_b, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b, NVFP4
+from .fp4_gemm import (Fp4Operand, gemm_allgather_transposed_b, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b,
+                       gemm_partials_transposed_b, reduce_partials, NVFP4)
 
 
 def shard_bounds(n: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
@@ -119,3 +120,85 @@ class ShardedFp4Linear:
         if self.world > 1:
             dist.all_gather_into_tensor(self._gathered.view(-1, n_local), local, group=self.group)
         return self._gathered
+
+
+def k_shard_bounds(k: int, world: int, rank: int, align: int = 256) -> tuple[int, int]:
+    """K-elements [lo, hi) of the operands owned by `rank` in the K-sharded (row-parallel) layer; every shard is a
+    multiple of `align` (whole scale blocks and whole 128-byte operand rows of the kernel's K stage)."""
+    return shard_bounds(k, world, rank, align)
+
+
+def slab_offsets(world: int, rank: int, rows_per_rank: int, n: int) -> list[int]:
+    """Byte offset, inside EVERY rank's (world, rows_per_rank, n) fp32 staging buffer, of the slab `rank` writes;
+    returned once per destination rank for symmetry with the pointer list the kernel takes."""
+    if not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}.")
+    return [rank * rows_per_rank * n * 4 for _ in range(world)]
+
+
+class RowShardedFp4Linear:
+    """Row-parallel ``y = x @ W.T`` with W (N, K) and x (M, K) sharded along K, followed by a reduce-scatter over
+    the rows of y: rank j ends up with ``y[j*M/w:(j+1)*M/w]`` (bf16), summed over all ranks' K-slices in rank order.
+
+    The typical producer of the K-sliced activation is the column-parallel layer before it (``ShardedFp4Linear``
+    without its all-gather, or the quantising epilogue): rank r's output columns are exactly its K-slice here.
+    NVFP4 tensor scales may differ per rank (each partial carries its own); MXFP4 has none.
+
+    fused=True: the GEMM epilogue stores every fp32 partial tile straight into the owner rank's staging buffer
+    (symmetric memory, plain peer stores over NVLink), device-side barriers bracket the step and a small kernel sums the
+    `world` slabs in rank order.  fused=False: partials stay local and NCCL reduce-scatters them in fp32.
+    """
+
+    def __init__(self, weight_kshard: Fp4Operand, group=None, fused: bool = True):
+        self.weight = weight_kshard
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.fused = bool(fused) and self.world > 1
+        self._staging: torch.Tensor | None = None
+        self._hdl = None
+        self._ptrs: list[int] = []
+        self._sum: torch.Tensor | None = None
+
+    def _buffers(self, m: int, n: int, device: torch.device) -> None:
+        rows = m // self.world
+        shape = (self.world, rows, n)
+        if self._staging is not None and tuple(self._staging.shape) == shape:
+            return
+        offs = slab_offsets(self.world, self.rank, rows, n)
+        if self.fused:
+            try:
+                import torch.distributed._symmetric_memory as symm
+
+                self._staging = symm.empty(shape, dtype=torch.float32, device=device)
+                self._hdl = symm.rendezvous(self._staging, self.group if self.group is not None else dist.group.WORLD)
+                self._ptrs = [int(self._hdl.buffer_ptrs[j]) + offs[j] for j in range(self.world)]
+                return
+            except Exception as exc:  # no peer-mapped memory on this system
+                import warnings
+
+                warnings.warn(f"symmetric memory is unavailable ({exc!r}); RowShardedFp4Linear uses the NCCL reduce-scatter")
+                self.fused = False
+                self._hdl = None
+        # local staging: slab j = this rank's partial of rank j's rows; reduced across ranks by NCCL
+        self._staging = torch.empty(shape, dtype=torch.float32, device=device)
+        self._ptrs = [self._staging.data_ptr() + j * rows * n * 4 for j in range(self.world)]
+        self._sum = torch.empty((1, rows, n), dtype=torch.float32, device=device)
+
+    def forward(self, x_kshard: Fp4Operand, bias: torch.Tensor | None = None, activation: str | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """Returns this rank's (M / world, N) bf16 rows of ``act(x @ W.T + bias)``."""
+        m, n = x_kshard.rows, self.weight.rows
+        if m % (32 * self.world) != 0:
+            raise ValueError(f"M must be a multiple of 32 * world = {32 * self.world}, got {m}.")
+        self._buffers(m, n, x_kshard.device)
+        if self.fused:
+            self._hdl.barrier()      # every rank has finished reading its staging buffer from the previous step
+            gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs)
+            self._hdl.barrier()      # every rank's partials have landed
+            return reduce_partials(self._staging, out=out, bias=bias, activation=activation)
+        gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs)
+        if self.world > 1:
+            dist.reduce_scatter_tensor(self._sum[0], self._staging.view(-1, n), op=dist.ReduceOp.SUM, group=self.group)
+            return reduce_partials(self._sum, out=out, bias=bias, activation=activation)
+        return reduce_partials(self._staging, out=out, bias=bias, activation=activation)

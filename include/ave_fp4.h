@@ -206,6 +206,26 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
                            int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt, int variant, void* stream);
 
 /*
+ * K-sharded GEMM + reduce-scatter in two calls (row-parallel linear layer on one NVLink/NVSwitch box).  No counterpart
+ * in the reference, which has no multi-GPU code.
+ *
+ * ave_fp4_gemm_partials: this rank holds the K-slices A (m, k) and B (n, k) of the full operands; the fp32 product
+ * (tensor scales applied, no rounding) is scattered by the epilogue's own stores: rows [j*m/world, (j+1)*m/world)
+ * go, row stride n, to slab_dst[j] -- a device pointer valid on THIS GPU to the (m/world, n) fp32 slab this rank owns
+ * inside rank j's staging buffer (peer-mapped memory for j != this rank, plain stores over NVLink; `slab_dst` is a host
+ * array read during the call).  m % (32 * world) == 0; 256x256 CTA-pair tiles.
+ *
+ * ave_fp4_reduce_partials: after every rank's partials have landed (the caller synchronises the ranks), the owner sums
+ * its `world` slabs (fp32 (rows, n), back to back, in slab order -- deterministic), applies the optional bias and
+ * activation, and rounds to bf16 once.
+ */
+int ave_fp4_gemm_partials(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int64_t m,
+                          int64_t n, int64_t k, int fmt, void* stream);
+int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int64_t n, void* d_bf16, int64_t ldd,
+                            const ave_fp4_epilogue* epilogue, void* stream);
+
+/*
  * Decode GEMM (M <= 16, N <= 65536) that allocates nothing and needs no caller workspace.
  * It has no counterpart in the reference.  It exists for hosts that cannot call cudaMalloc:
  * a plugin living inside another runtime's memory pool, or a serving loop that must not risk

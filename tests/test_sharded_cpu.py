@@ -68,3 +68,71 @@ def test_gather_layout_two_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert ret[0] and ret[1]
+
+
+def test_k_shard_bounds_and_slab_offsets():
+    assert sharded.k_shard_bounds(8192, 8, 3) == (3072, 4096)
+    spans = [sharded.k_shard_bounds(8192, 4, r) for r in range(4)]
+    assert spans[0][0] == 0 and spans[-1][1] == 8192 and all(spans[i][1] == spans[i + 1][0] for i in range(3))
+    with pytest.raises(ValueError):
+        sharded.k_shard_bounds(1000, 4, 0)
+    # rank 2 of 4 writes slab 2 of every (4, rows, n) fp32 staging buffer
+    assert sharded.slab_offsets(4, 2, 64, 1024) == [2 * 64 * 1024 * 4] * 4
+    with pytest.raises(ValueError):
+        sharded.slab_offsets(4, 4, 64, 1024)
+
+
+def _k_worker(rank, world, port, ret):
+    """The K-sharded layer's arithmetic on two gloo ranks, with the oracle as the per-rank GEMM: every rank's fp32
+    partial (its K-slice, its own tensor scales) is placed in the owner's slab, slabs are summed in rank order."""
+    import numpy as np
+
+    from oracle import fp4_oracle as O
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n, k = 64, 48, 512
+        g = torch.Generator().manual_seed(3)
+        a = torch.randn((m, k), generator=g).to(torch.bfloat16)
+        w = (torch.randn((n, k), generator=g) * 0.02).to(torch.bfloat16)
+        bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+        lo, hi = sharded.k_shard_bounds(k, world, rank)
+        qa, qw = O.c_quantize(bits(a[:, lo:hi]), O.NVFP4), O.c_quantize(bits(w[:, lo:hi]), O.NVFP4)
+        part, _ = O.c_gemm_fp4(qa, qw, O.NVFP4)                       # (m, n) fp32, this rank's K-slice
+        rows = m // world
+        staging = [torch.zeros((world, rows, n)) for _ in range(world)]   # staging[j] lives on rank j
+        # "peer stores": all-gather the partials, then every rank fills its own staging buffer from them
+        parts = [torch.zeros((m, n)) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(part))
+        mine = torch.stack([parts[r][rank * rows:(rank + 1) * rows] for r in range(world)])   # (world, rows, n)
+        total = torch.zeros((rows, n))
+        for r in range(world):
+            total += mine[r]
+        got = total.to(torch.bfloat16)
+        # the unsharded oracle on per-shard-quantised operands: dequantise each K-slice, one fp32 matmul
+        deq_a = np.concatenate([O.c_dequantize(*O.c_quantize(bits(a[:, s:e]), O.NVFP4), O.NVFP4)
+                                for s, e in (sharded.k_shard_bounds(k, world, r) for r in range(world))], axis=1)
+        deq_w = np.concatenate([O.c_dequantize(*O.c_quantize(bits(w[:, s:e]), O.NVFP4), O.NVFP4)
+                                for s, e in (sharded.k_shard_bounds(k, world, r) for r in range(world))], axis=1)
+        full = torch.from_numpy(deq_a) @ torch.from_numpy(deq_w).T
+        exp = full[rank * rows:(rank + 1) * rows].to(torch.bfloat16)
+        rel = float((got.float() - exp.float()).norm() / exp.float().norm())
+        ret[rank] = rel < 1e-3
+    finally:
+        dist.destroy_process_group()
+
+
+def test_k_sharded_reduce_scatter_math_two_ranks():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_k_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert ret[0] and ret[1]
