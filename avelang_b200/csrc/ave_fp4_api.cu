@@ -56,6 +56,10 @@ struct DeviceState {
     int* status = nullptr;
     long long* trace = nullptr;  // optional profiling buffer set by ave_fp4_set_trace
     int trace_cap = 0;
+    // resident 256-thread blocks per SM of the streaming kernels: their grids are exactly one wave
+    int occ_amax = 1;
+    int occ_quant[2][2] = {{1, 1}, {1, 1}};   // [format][tiled]
+    int occ_reduce = 1;
 };
 
 std::mutex g_mutex;
@@ -520,6 +524,20 @@ int ave_fp4_init(int device) {
     AVE_CUDA(cudaMemset(status, 0, sizeof(int)));
     g_dev[device].status = status;
     g_dev[device].sm_count = prop.multiProcessorCount;
+    {
+        DeviceState& d = g_dev[device];
+        auto occ = [](auto kernel) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) n = 1;
+            return n;
+        };
+        d.occ_amax = occ(amax_bf16_kernel);
+        d.occ_quant[0][0] = occ(quantize_fp4_kernel<kFmtNvfp4, false>);
+        d.occ_quant[0][1] = occ(quantize_fp4_kernel<kFmtNvfp4, true>);
+        d.occ_quant[1][0] = occ(quantize_fp4_kernel<kFmtMxfp4, false>);
+        d.occ_quant[1][1] = occ(quantize_fp4_kernel<kFmtMxfp4, true>);
+        d.occ_reduce = occ(reduce_partials_kernel);
+    }
     g_dev[device].ready = true;
     AVE_CUDA(cudaSetDevice(prev));
     return 0;
@@ -557,7 +575,7 @@ int ave_fp4_amax(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, void*
     const long long groups = rows * (k / 8);
     if (groups == 0) return 0;
     long long blocks = (groups + 255) / 256;
-    const long long cap = static_cast<long long>(ds->sm_count) * 8;
+    const long long cap = static_cast<long long>(ds->sm_count) * ds->occ_amax;   // one full wave
     if (blocks > cap) blocks = cap;
     amax_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), rows, k, ldx,
                                                                    static_cast<unsigned int*>(amax_f32));
@@ -589,8 +607,8 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
     const long long rows_pad = tiled ? ((rows + 127) / 128) * 128 : rows;
     const long long items = rows_pad * ((k + 1023) / 1024);  // one warp step each
     long long blocks = (items + 7) / 8;
-    const long long cap = static_cast<long long>(ds->sm_count) * 8;
-    if (blocks > cap) blocks = cap;
+    const long long cap = static_cast<long long>(ds->sm_count) * ds->occ_quant[fmt == AVE_FP4_FMT_NVFP4 ? 0 : 1][tiled ? 1 : 0];
+    if (blocks > cap) blocks = cap;   // one full wave of resident blocks; each walks the items with a grid stride
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(x_bf16);
     const unsigned int* amax = static_cast<const unsigned int*>(amax_f32);
     float* gs = static_cast<float*>(global_scale);
@@ -818,7 +836,7 @@ int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int6
     }
     const long long groups = rows * (n / 8);
     long long blocks = (groups + 255) / 256;
-    const long long cap = static_cast<long long>(ds->sm_count) * 8;
+    const long long cap = static_cast<long long>(ds->sm_count) * ds->occ_reduce;
     if (blocks > cap) blocks = cap;
     reduce_partials_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float*>(slabs_f32), world, rows, n, static_cast<__nv_bfloat16*>(d_bf16), ldd, bias, act);

@@ -33,7 +33,9 @@ amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long 
     const long long groups_per_row = k / 8;
     const long long total = rows * groups_per_row;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    float a = 0.0f;
+    // running maximum of the bf16 magnitudes as packed unsigned 16-bit pairs (finite bf16 magnitudes order like integers)
+    constexpr uint32_t kMag = 0x7fff7fffu;
+    uint32_t m = 0;
     // four independent 128-bit loads in flight per thread
     for (long long g0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g0 < total; g0 += 4 * stride) {
         uint4 v[4];
@@ -42,24 +44,23 @@ amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long 
             const long long g = g0 + u * stride;
             v[u] = make_uint4(0, 0, 0, 0);
             if (g < total) {
-                const long long r = g / groups_per_row;
-                const long long c = g - r * groups_per_row;
-                v[u] = __ldcs(reinterpret_cast<const uint4*>(x + r * ldx + c * 8));
+                long long off = g * 8;          // rows back to back: no division
+                if (ldx != k) {
+                    const long long r = g / groups_per_row;
+                    off = r * ldx + (g - r * groups_per_row) * 8;
+                }
+                v[u] = __ldcs(reinterpret_cast<const uint4*>(x + off));
             }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                a = fmaxf(a, fabsf(__uint_as_float(w[i] << 16)));
-                a = fmaxf(a, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
-            }
+            m = __vimax3_u16x2(m, v[u].x & kMag, v[u].y & kMag);
+            m = __vimax3_u16x2(m, v[u].z & kMag, v[u].w & kMag);
         }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    if ((threadIdx.x & 31) == 0 && a > 0.0f) atomicMax(amax_bits, __float_as_uint(a));
+    uint32_t a = max(m & 0xffffu, m >> 16);
+    a = __reduce_max_sync(0xffffffffu, a);
+    if ((threadIdx.x & 31) == 0 && a != 0) atomicMax(amax_bits, a << 16);   // fp32 bit pattern of the bf16 maximum
 }
 
 __device__ __forceinline__ float e4m3_decode(uint32_t c) {
@@ -83,6 +84,29 @@ __device__ __forceinline__ uint32_t pack8_e2m1(const float (&y)[8]) {
         w |= static_cast<uint32_t>(b) << (8 * i);
     }
     return w;
+}
+
+// The same for four (even, odd) element pairs.
+__device__ __forceinline__ uint32_t pack8_e2m1_pairs(const float2 (&y)[4]) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_fp4x2_storage_t b = __nv_cvt_float2_to_fp4x2(y[i], __NV_E2M1, cudaRoundNearest);
+        w |= static_cast<uint32_t>(b) << (8 * i);
+    }
+    return w;
+}
+
+// max |x| over N words of bf16 pairs, as the bf16 bit pattern of the maximum (magnitudes of finite bf16 values
+// order like unsigned 16-bit integers): one AND per word and one three-input packed maximum per two words.
+template <int N>
+__device__ __forceinline__ uint32_t block_amax_bits(const uint32_t* __restrict__ rw) {
+    constexpr uint32_t kMag = 0x7fff7fffu;
+    uint32_t m = rw[0] & kMag;
+#pragma unroll
+    for (int i = 1; i + 1 < N; i += 2) m = __vimax3_u16x2(m, rw[i] & kMag, rw[i + 1] & kMag);
+    if ((N & 1) == 0) m = __vimax3_u16x2(m, rw[N - 1] & kMag, 0u);
+    return max(m & 0xffffu, m >> 16);
 }
 
 // FMT: kFmtNvfp4 (16-element blocks, E4M3 scale relative to the tensor scale gs) or
@@ -115,12 +139,7 @@ template <int FMT>
 __device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ rw, float gs, bool gs_plain, float gs_recip,
                                                    float sixth, uint32_t* __restrict__ out_words) {
     constexpr int BLK = (FMT == kFmtNvfp4) ? 16 : 32;
-    float a = 0.0f;
-#pragma unroll
-    for (int i = 0; i < BLK / 2; ++i) {
-        a = fmaxf(a, fabsf(__uint_as_float(rw[i] << 16)));
-        a = fmaxf(a, fabsf(__uint_as_float(rw[i] & 0xffff0000u)));
-    }
+    const float a = __uint_as_float(block_amax_bits<BLK / 2>(rw) << 16);
     uint32_t code;
     if (FMT == kFmtNvfp4) {
         // 6 is a plain divisor; a quotient in the subnormal range takes the plain division
@@ -131,16 +150,24 @@ __device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ 
         // one of three paths per block, chosen outside the element loops: the common one (reciprocal
         // division), all-zero block scale, and the rare divisors that need the plain division
         if (d != 0.0f && divisor_is_plain(d)) {
-            const float rd = __frcp_rn(d);
+            // x / d by the reciprocal (see div_by_recip), two elements per instruction with the packed fp32
+            // multiply and FMA of sm_100, and computed as -(x / d): with nr = -RN(1/d), q0 = x*nr, t = x + q0*d,
+            // -q = q0 + t*nr.  Every step is the mirror image of the positive-sign sequence, so the rounding is
+            // the same, and a zero quotient comes out with the sign opposite to x's in every case (x = -0
+            // included), which the final XOR of the eight sign bits turns into x's sign -- no per-element fix-up.
+            const float nr = -__frcp_rn(d);
+            const float2 d2 = make_float2(d, d), nr2 = make_float2(nr, nr);
 #pragma unroll
             for (int w = 0; w < BLK / 8; ++w) {
-                float y[8];
+                float2 y[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    y[2 * i] = div_by_recip(__uint_as_float(rw[w * 4 + i] << 16), d, rd);
-                    y[2 * i + 1] = div_by_recip(__uint_as_float(rw[w * 4 + i] & 0xffff0000u), d, rd);
+                    const float2 x2 = make_float2(__uint_as_float(rw[w * 4 + i] << 16), __uint_as_float(rw[w * 4 + i] & 0xffff0000u));
+                    const float2 q0 = __fmul2_rn(x2, nr2);
+                    const float2 t = __ffma2_rn(q0, d2, x2);
+                    y[i] = __ffma2_rn(t, nr2, q0);
                 }
-                out_words[w] = pack8_e2m1(y);
+                out_words[w] = pack8_e2m1_pairs(y) ^ 0x88888888u;
             }
         } else if (d == 0.0f) {
 #pragma unroll
@@ -175,15 +202,14 @@ __device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ 
             code = static_cast<uint32_t>(max(E - 2, 0));
         }
         const float inv = __uint_as_float((254u - code) << 23);  // 2^(127-code), exact scaling
+        const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
         for (int w = 0; w < BLK / 8; ++w) {
-            float y[8];
+            float2 y[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                y[2 * i] = __fmul_rn(__uint_as_float(rw[w * 4 + i] << 16), inv);
-                y[2 * i + 1] = __fmul_rn(__uint_as_float(rw[w * 4 + i] & 0xffff0000u), inv);
-            }
-            out_words[w] = pack8_e2m1(y);
+            for (int i = 0; i < 4; ++i)
+                y[i] = __fmul2_rn(make_float2(__uint_as_float(rw[w * 4 + i] << 16), __uint_as_float(rw[w * 4 + i] & 0xffff0000u)), inv2);
+            out_words[w] = pack8_e2m1_pairs(y);
         }
     }
     return code;
@@ -213,9 +239,14 @@ __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ 
     const int chunks = (k_pad + 1023) / 1024;
     const long long items = rows_pad * chunks;
 
-    for (long long item = warp_global; item < items; item += warps_total) {
-        const long long r = item / chunks;
-        const int e = static_cast<int>(item - r * chunks) * 1024 + lane * 32;   // this lane's first element
+    // (row, chunk) of the current item, advanced without a division per item
+    long long r = warp_global / chunks;
+    int ch = static_cast<int>(warp_global - r * chunks);
+    const long long step_r = warps_total / chunks;
+    const int step_c = static_cast<int>(warps_total - step_r * chunks);
+    for (long long item = warp_global; item < items; item += warps_total, r += step_r, ch += step_c) {
+        if (ch >= chunks) { ch -= chunks; ++r; }
+        const int e = ch * 1024 + lane * 32;   // this lane's first element
         const int c = e / BLK;                                                  // ... and first scale column
         const bool in = (r < rows) && (e < kk);
         if (!in) {

@@ -149,3 +149,24 @@ def test_quantize_static_scales_fuzz(cuda_device, oracle, gs):
     ep, es, _ = oracle.c_quantize(_bits(x), oracle.NVFP4, global_scale=float(np.float32(gs)))
     assert np.array_equal(q.scales.cpu().numpy(), es)
     assert np.array_equal(q.packed.cpu().numpy(), ep)
+
+
+@pytest.mark.parametrize("fmt", [ave.NVFP4, ave.MXFP4])
+def test_quantize_signed_zeros_and_tiny_values(cuda_device, oracle, fmt):
+    """Zeros of both signs, bf16 subnormals and values far below the block scale, scattered through blocks whose
+    scale is not zero: the nibble keeps the sign of x even when the magnitude rounds to zero."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn((64, 1024), generator=g)
+    pick = torch.rand((64, 1024), generator=g)
+    x[pick < 0.10] = 0.0
+    x[(pick >= 0.10) & (pick < 0.20)] = -0.0
+    x[(pick >= 0.20) & (pick < 0.25)] = 1e-39          # bf16 subnormal
+    x[(pick >= 0.25) & (pick < 0.30)] = -1e-39
+    x[(pick >= 0.30) & (pick < 0.35)] *= 1e-6
+    x = x.to(torch.bfloat16)
+    assert (x.view(torch.int16) == -32768).any()        # -0 survived the cast
+    ep, es, eg = oracle.c_quantize(_bits(x), fmt)
+    q = _q(x.to(cuda_device), fmt, ave.SF_ROW_MAJOR)
+    ave.check_device_status(cuda_device)
+    assert np.array_equal(q.packed.cpu().numpy(), ep)
+    assert np.array_equal(q.scales.cpu().numpy(), es)
