@@ -386,7 +386,10 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
     variant &= ~AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS;
     if (variant == AVE_FP4_GEMM_SKINNY_TILED_W) return AVE_FP4_GEMM_SKINNY;
     if (variant != AVE_FP4_GEMM_AUTO) return variant;
-    if (m <= 64) return AVE_FP4_GEMM_SKINNY;
+    // Decode kernel up to 32 rows.  From 33 rows on the 128x128 tiles are as fast or faster even for weight-streaming
+    // shapes (measured at 64 rows: 28.1 vs 30.9 us for 28672 x 8192, 13.7 vs 20.8 us for 8192 x 8192): the stream-K
+    // partial sums grow with the row count (64 rows: 32 KB per partial tile) while a 128-row tile costs the same for any M.
+    if (m <= 32) return AVE_FP4_GEMM_SKINNY;
     // Tiled kernels: estimate the time of each tile shape as (waves of tiles over the SMs) x (tile work) /
     // (how well that shape feeds the tensor pipe, measured at 8192^3), and take the smallest.  Large problems
     // get 256x256 CTA-pair tiles; problems with few tiles get smaller tiles so that more SMs have work.

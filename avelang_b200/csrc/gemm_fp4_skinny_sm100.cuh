@@ -19,6 +19,8 @@
 
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 #include "gemm_fp4_sm100.cuh"
 
 namespace avefp4 {
@@ -65,8 +67,9 @@ struct SkinnyConfig {
     static constexpr int kTmemSfw = kAccStages * MP;
     static constexpr int kTmemSfx = kTmemSfw + kSfK * 4;
     static constexpr int kTmemUsed = kTmemSfx + kSfK * 4;
-    static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : 256;
-    static_assert(MP % 16 == 0 && MP >= 16 && MP <= 64, "MP must be 16, 32, 48 or 64");
+    static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : kTmemUsed <= 256 ? 256 : 512;
+    static_assert(MP % 16 == 0 && MP >= 16 && MP <= 128, "MP must be a multiple of 16 up to 128");
+    static_assert(kTmemUsed <= 512, "tensor memory budget");
     static_assert((MP * 128) % 1024 == 0, "activation tile must keep 1024-byte alignment of later stages");
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
@@ -308,12 +311,6 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         float alpha = 1.0f;
         if (p.x_gs) alpha *= __ldcg(p.x_gs);
         if (p.w_gs) alpha *= __ldcg(p.w_gs);
-        // tensor scales, then the optional fused bias (per weight row = output column) and activation
-        auto finish = [&](float acc, int col) -> float {
-            if (p.bias == nullptr && p.act == kActNone) return acc * alpha;
-            const float b = (p.bias != nullptr) ? __bfloat162float(p.bias[col]) : 0.0f;
-            return activate_rt(fmaf(acc, alpha, b), p.act);
-        };
         int seg = 0;
         bool ok = true;
         for (long long u = u_begin; u < u_end && ok; ++seg) {
@@ -346,13 +343,10 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             const long long te2 = tr ? clock64() : 0;
             const int n = tile * 128 + n_local;
             const bool whole = (kb0 == 0 && kb1 == num_kb);
-            if (whole) {
-                if (n < p.n) {
-#pragma unroll
-                    for (int m = 0; m < MP; ++m)
-                        if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(finish(__uint_as_float(v[m]), n));
-                }
-            } else {
+            // `v` ends up holding the complete fp32 sums of this thread's weight row when `final_here` is set:
+            // at once for a whole tile, or after the last contributor has added up the partials.
+            bool final_here = whole;
+            if (!whole) {
                 const int slot = (kb0 == 0) ? 1 : 0;
                 float* mine = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MP * 128);
 #pragma unroll
@@ -375,18 +369,40 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 if (f >= 0) {
                     __threadfence();
                     const int c0 = f & 0xffff, c1 = f >> 16;
-                    float sum[MP];
 #pragma unroll
-                    for (int m = 0; m < MP; ++m) sum[m] = 0.0f;
+                    for (int m = 0; m < MP; ++m) v[m] = 0u;   // +0.0f
                     for (int c = c0; c <= c1; ++c) {
                         const float* src = p.partials + (static_cast<size_t>(c) * 2 + (c == c0 ? 1 : 0)) * (MP * 128);
 #pragma unroll
-                        for (int m = 0; m < MP; ++m) sum[m] += __ldcg(src + m * 128 + n_local);
+                        for (int m = 0; m < MP; ++m) v[m] = __float_as_uint(__uint_as_float(v[m]) + __ldcg(src + m * 128 + n_local));
                     }
-                    if (n < p.n) {
+                    final_here = true;
+                }
+            }
+            // One write-out for both cases, and the epilogue choice made outside the unrolled loops: the plain
+            // path stays a compact run of multiply-convert-store (the unrolled code of this kernel is large enough
+            // for instruction fetch to show up in a ~20 us kernel).
+            if (final_here && n < p.n) {
+                __nv_bfloat16* dst = p.d + n;
+                if (p.bias == nullptr && p.act == kActNone) {
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        if (m < p.m) dst[static_cast<size_t>(m) * p.ldd] = __float2bfloat16_rn(__uint_as_float(v[m]) * alpha);
+                } else {
+                    const float b = (p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
+                    auto store_act = [&](auto act_tag) {
+                        constexpr int ACT = decltype(act_tag)::value;
 #pragma unroll
                         for (int m = 0; m < MP; ++m)
-                            if (m < p.m) p.d[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16_rn(finish(sum[m], n));
+                            if (m < p.m)
+                                dst[static_cast<size_t>(m) * p.ldd] = __float2bfloat16_rn(activate<ACT>(fmaf(__uint_as_float(v[m]), alpha, b)));
+                    };
+                    switch (p.act) {
+                        case kActRelu: store_act(std::integral_constant<int, kActRelu>{}); break;
+                        case kActGelu: store_act(std::integral_constant<int, kActGelu>{}); break;
+                        case kActGeluTanh: store_act(std::integral_constant<int, kActGeluTanh>{}); break;
+                        case kActSilu: store_act(std::integral_constant<int, kActSilu>{}); break;
+                        default: store_act(std::integral_constant<int, kActNone>{}); break;
                     }
                 }
             }

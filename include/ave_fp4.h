@@ -54,7 +54,7 @@ extern "C" {
 #define AVE_FP4_GEMM_2CTA_N256 3 /* CTA pair, 256x256 tile */
 #define AVE_FP4_GEMM_2CTA_N128 4 /* CTA pair, 256x128 tile, two accumulator buffers */
 #define AVE_FP4_GEMM_2CTA_N192 5 /* CTA pair, 256x192 tile, two accumulator buffers */
-#define AVE_FP4_GEMM_SKINNY 10   /* M <= 64: operands swapped, stream-K over all SMs */
+#define AVE_FP4_GEMM_SKINNY 10   /* M <= 64 (chosen by default up to M = 32): operands swapped, stream-K over all SMs */
 #define AVE_FP4_GEMM_SKINNY_TILED_W 11 /* as 10, with b_packed in the tile-major layout of ave_fp4_pack_weight_tiles */
 
 /*

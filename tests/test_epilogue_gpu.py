@@ -57,7 +57,7 @@ def test_ragged_with_epilogue(cuda_device, oracle, m, n, k):
 def test_decode_kernel_with_epilogue(cuda_device, oracle, m, n, k, act):
     """Decode kernel: the bias runs along the weight rows (the tensor core's M axis after the operand swap);
     both the whole-tile and the stream-K partial-sum write-outs apply it."""
-    _case(oracle, cuda_device, ave.NVFP4, m, n, k, ave.GEMM_AUTO, act, True)
+    _case(oracle, cuda_device, ave.NVFP4, m, n, k, ave.GEMM_SKINNY, act, True)
 
 
 def test_argument_errors(cuda_device, oracle):
@@ -156,3 +156,27 @@ def test_quantised_result_argument_errors(cuda_device):
         ave.gemm_quantized_out_transposed_b(A, B, None)
     with pytest.raises(ValueError):
         ave.gemm_quantized_out_transposed_b(A, B, gs, variant=ave.GEMM_SKINNY)
+
+
+def test_epilogues_inside_cuda_graph(cuda_device):
+    """The fused-epilogue entry points are capturable like the plain operator (the reference benchmark captures its
+    operator call the same way, benchmark/gemm/bench_amdgpu_gemm.py:37-41): no allocation, sync or host read inside."""
+    A, B, bias = _operands(cuda_device, ave.NVFP4, 256, 512, 1024)
+    out = torch.empty((256, 512), dtype=torch.bfloat16, device=cuda_device)
+    ref = ave.gemm_nvfp4_transposed_b(A, B, bias=bias, activation="gelu")
+    gs = (ref.float().abs().max() / 2688.0).reshape(1)
+    qref = ave.quantize_nvfp4(ref, global_scale=gs)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.graph(graph, stream=stream):
+        ave.gemm_nvfp4_transposed_b(A, B, out=out, bias=bias, activation="gelu")
+        q = ave.gemm_quantized_out_transposed_b(A, B, gs, bias=bias, activation="gelu")
+    out.zero_()
+    q.packed.zero_()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    ave.check_device_status(cuda_device)
+    assert torch.equal(out, ref)
+    assert torch.equal(q.packed, qref.packed) and torch.equal(q.scales, qref.scales)
