@@ -6,12 +6,14 @@
 // (TMEM lanes) and the few activation rows on the MMA N axis (TMEM columns), so a
 // 128 x MP x 64 tcgen05.mma does the work without padding M up to 128.
 //
-// Work is split stream-K style: the (weight tile, K block) units are cut into
-// gridDim.x equal contiguous ranges, one per persistent CTA, so every SM pulls the
-// same number of bytes.  A range that covers only part of a tile's K writes an fp32
-// partial to scratch memory; the CTA that completes a tile last (per-tile arrival
-// counter) adds the partials in a fixed order and writes the bf16 result, so the
-// output is deterministic and nobody waits on another CTA.
+// Work is split so that every SM pulls the same number of bytes, in two phases.  With T weight
+// tiles and G persistent CTAs, the first T mod G tiles are split stream-K style: their (tile, K block)
+// units are cut into G equal contiguous ranges, one per CTA.  A range that covers only part of a
+// tile's K writes an fp32 partial to scratch memory; the CTA that completes a tile last (per-tile
+// arrival counter) adds the partials in a fixed order and writes the bf16 result, so the output is
+// deterministic and nobody waits on another CTA.  After its range every CTA computes floor(T / G)
+// whole tiles of its own.  The stream-K part comes first, so its partial-sum round trips run under
+// the following tiles' loads, and the kernel ends with a plain whole-tile write-out.
 //
 // Plays the role of python/avelang_kernels/amdgpu_gemm.py:349-455 for the shapes
 // the reference tile (128x128) cannot fill.
@@ -94,10 +96,13 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
-    const long long units = static_cast<long long>(p.tiles_n) * num_kb;
     const long long ctas = gridDim.x;
+    const int whole_tiles = p.tiles_n / static_cast<int>(gridDim.x);            // whole tiles per CTA (second phase)
+    const int sk_tiles = p.tiles_n - whole_tiles * static_cast<int>(gridDim.x);  // tiles 0 .. sk_tiles-1 are split stream-K
+    const long long units = static_cast<long long>(sk_tiles) * num_kb;           // stream-K units, cut into equal ranges
     const long long u_begin = (static_cast<long long>(blockIdx.x) * units) / ctas;
     const long long u_end = (static_cast<long long>(blockIdx.x + 1) * units) / ctas;
+    const int first_whole = sk_tiles + static_cast<int>(blockIdx.x);              // then tiles first_whole + j * G
 
     const uint32_t bar_full = smem_base + Cfg::kOffBar;
     const uint32_t bar_empty = bar_full + STAGES * 8;
@@ -158,7 +163,16 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             // (tile, K block) of the next unit, advanced incrementally (no division in the loop)
             int tile = static_cast<int>(u_begin / num_kb);
             int kb = static_cast<int>(u_begin - static_cast<long long>(tile) * num_kb);
-            int left = static_cast<int>(u_end - u_begin);
+            int left_sk = static_cast<int>(u_end - u_begin);               // units left in the stream-K range
+            if (left_sk == 0) { tile = first_whole; kb = 0; }
+            int left = left_sk + whole_tiles * num_kb;
+            const int tile_step = static_cast<int>(gridDim.x);
+            // next unit after (t, k): inside the stream-K range the next K block or tile; after its last unit the
+            // first whole tile; among the whole tiles every gridDim.x-th tile
+            auto advance = [&](int& t, int& k, int& lsk) {
+                if (lsk > 0 && --lsk == 0) { t = first_whole; k = 0; return; }
+                if (++k == num_kb) { k = 0; t += (lsk > 0) ? 1 : tile_step; }
+            };
             while (left > 0 && ok) {
                 const long long t0 = tr ? clock64() : 0;
                 const int g = left < p.burst ? left : p.burst;
@@ -174,7 +188,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 const long long t1 = tr ? clock64() : 0;
                 if (issuer) {
                     // weight tiles first: neighbouring K blocks of the same rows go out back to back
-                    int s = stage, t = tile, k = kb;
+                    int s = stage, t = tile, k = kb, lsk = left_sk;
 #pragma unroll
                     for (int i = 0; i < kBurst; ++i) {
                         if (i < g) {
@@ -186,7 +200,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                                 tma_load_2d<1, 1>(smem_base + Cfg::kOffW + s * Cfg::kWBytes, &tm_w, bar_full + s * 8, k * 128,
                                                t * 128);
                             if (++s == STAGES) s = 0;
-                            if (++k == num_kb) { k = 0; ++t; }
+                            advance(t, k, lsk);
                         }
                     }
                     // the activations (and their scales) may come from the previous kernel: wait for it
@@ -195,7 +209,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                         pdl_wait_prior_grid();
                         prior_done = true;
                     }
-                    s = stage; t = tile; k = kb;
+                    s = stage; t = tile; k = kb; lsk = left_sk;
 #pragma unroll
                     for (int i = 0; i < kBurst; ++i) {
                         if (i < g) {
@@ -205,7 +219,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                             tma_load_2d<1, 2>(smem_base + Cfg::kOffX + s * Cfg::kXBytes, &tm_x, full, k * 128, 0);
                             tma_load_2d<1, 2>(smem_base + Cfg::kOffSfx + s * Cfg::kSfBytes, &tm_sfx, full, 0, k * Cfg::kSfK);
                             if (++s == STAGES) s = 0;
-                            if (++k == num_kb) { k = 0; ++t; }
+                            advance(t, k, lsk);
                         }
                     }
                     if (tr && rec < p.trace_cap) {
@@ -217,8 +231,7 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 left -= g;
                 stage += g;
                 if (stage >= STAGES) { stage -= STAGES; phase ^= 1u; }
-                kb += g;
-                while (kb >= num_kb) { kb -= num_kb; ++tile; }
+                for (int i = 0; i < g; ++i) advance(tile, kb, left_sk);
             }
             if (ok) {
                 for (int i = 0; i < STAGES; ++i) {
@@ -242,10 +255,19 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             bool ok = true;
             const bool tr = (p.trace != nullptr) && (blockIdx.x == 0);
             int rec = 0;
-            for (long long u = u_begin; u < u_end && ok; ++seg) {
-                const int kb0 = static_cast<int>(u % num_kb);
-                const long long left = u_end - u;
-                const int kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
+            const int num_segs_whole = whole_tiles;
+            long long u = u_begin;
+            for (int done_whole = 0; (u < u_end || done_whole < num_segs_whole) && ok; ++seg) {
+                // segment = K blocks [kb0, kb1) of one tile: first the stream-K range, then the whole tiles
+                int kb0 = 0, kb1 = num_kb;
+                if (u < u_end) {
+                    kb0 = static_cast<int>(u % num_kb);
+                    const long long left = u_end - u;
+                    kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
+                    u += kb1 - kb0;
+                } else {
+                    ++done_whole;
+                }
                 const int acc = seg % ACC;
                 const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
                 if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
@@ -298,7 +320,6 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 }
                 if (ok && issuer) tcgen05_commit<1>(bar_tfull + acc * 8);
                 __syncwarp();
-                u += kb1 - kb0;
             }
         }
     } else {
@@ -313,12 +334,19 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         if (p.w_gs) alpha *= __ldcg(p.w_gs);
         int seg = 0;
         bool ok = true;
-        for (long long u = u_begin; u < u_end && ok; ++seg) {
-            const int tile = static_cast<int>(u / num_kb);
-            const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
-            const long long left = u_end - u;
-            const int kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
-            u += kb1 - kb0;
+        long long u = u_begin;
+        for (int done_whole = 0; (u < u_end || done_whole < whole_tiles) && ok; ++seg) {
+            int tile, kb0 = 0, kb1 = num_kb;
+            if (u < u_end) {
+                tile = static_cast<int>(u / num_kb);
+                kb0 = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
+                const long long left = u_end - u;
+                kb1 = (left < num_kb - kb0) ? kb0 + static_cast<int>(left) : num_kb;
+                u += kb1 - kb0;
+            } else {
+                tile = first_whole + done_whole * static_cast<int>(gridDim.x);
+                ++done_whole;
+            }
             const int acc = seg % ACC;
             const uint32_t acc_phase = static_cast<uint32_t>(seg / ACC) & 1u;
             const bool tr = (p.trace != nullptr) && (blockIdx.x == 0) && (warp == 2) && (lane == 0) && (seg < p.trace_cap);
