@@ -647,13 +647,24 @@ int ave_fp4_quantize_nvfp4_dynamic(const void* x_bf16, int64_t rows, int64_t k, 
             return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: tiled scales must be 4-byte aligned");
         cudaStream_t s = static_cast<cudaStream_t>(stream);
         const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(x_bf16);
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(kFusedClusterCtas, 1, 1);
+        cfg.blockDim = dim3(kFusedThreads, 1, 1);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits for its predecessor itself
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        long long rows_ll = rows, k_ll = k, ldx_ll = ldx;
+        float* gs = static_cast<float*>(global_scale);
+        uint8_t* pk = static_cast<uint8_t*>(packed);
+        uint8_t* sf = static_cast<uint8_t*>(scales);
         if (sf_layout == AVE_FP4_SF_TILED)
-            quantize_nvfp4_fused_small_kernel<true><<<kFusedClusterCtas, kFusedThreads, 0, s>>>(
-                x, rows, k, ldx, static_cast<float*>(global_scale), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales));
+            AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_nvfp4_fused_small_kernel<true>, x, rows_ll, k_ll, ldx_ll, gs, pk, sf));
         else
-            quantize_nvfp4_fused_small_kernel<false><<<kFusedClusterCtas, kFusedThreads, 0, s>>>(
-                x, rows, k, ldx, static_cast<float*>(global_scale), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales));
-        AVE_CUDA(cudaGetLastError());
+            AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_nvfp4_fused_small_kernel<false>, x, rows_ll, k_ll, ldx_ll, gs, pk, sf));
         return 0;
     }
     if (!amax_scratch) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_quantize_nvfp4_dynamic: amax_scratch (4 bytes) is needed above %lld elements",

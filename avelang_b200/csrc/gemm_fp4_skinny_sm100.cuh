@@ -175,7 +175,10 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             };
             while (left > 0 && ok) {
                 const long long t0 = tr ? clock64() : 0;
-                const int g = left < p.burst ? left : p.burst;
+                // the first burst fills the whole ring (every slot is free): all of these weight loads are in flight
+                // before the producer waits for the previous kernel's activations
+                const int want = (rec == 0) ? STAGES : p.burst;
+                const int g = left < want ? left : want;
                 // slots are released in order, so a free last slot means the whole burst is free
                 const int last = stage + g - 1;
                 const int last_stage = last >= STAGES ? last - STAGES : last;
@@ -199,6 +202,8 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                             else
                                 tma_load_2d<1, 1>(smem_base + Cfg::kOffW + s * Cfg::kWBytes, &tm_w, bar_full + s * 8, k * 128,
                                                t * 128);
+                            tma_load_2d<1, 1>(smem_base + Cfg::kOffSfw + s * Cfg::kSfBytes, &tm_sfw, bar_full + s * 8, 0,
+                                           t * p.w_sf_k_atoms + k * Cfg::kSfK);
                             if (++s == STAGES) s = 0;
                             advance(t, k, lsk);
                         }
@@ -214,8 +219,6 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                     for (int i = 0; i < kBurst; ++i) {
                         if (i < g) {
                             const uint32_t full = bar_full + s * 8;
-                            tma_load_2d<1, 1>(smem_base + Cfg::kOffSfw + s * Cfg::kSfBytes, &tm_sfw, full, 0,
-                                           t * p.w_sf_k_atoms + k * Cfg::kSfK);
                             tma_load_2d<1, 2>(smem_base + Cfg::kOffX + s * Cfg::kXBytes, &tm_x, full, k * 128, 0);
                             tma_load_2d<1, 2>(smem_base + Cfg::kOffSfx + s * Cfg::kSfBytes, &tm_sfx, full, 0, k * Cfg::kSfK);
                             if (++s == STAGES) s = 0;

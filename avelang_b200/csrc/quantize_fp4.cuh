@@ -317,7 +317,11 @@ quantize_nvfp4_fused_small_kernel(const __nv_bfloat16* __restrict__ x, long long
                                   float* __restrict__ gs_out, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
     __shared__ float s_warp[kFusedThreads / 32];
     __shared__ float s_cta;
+    // Launched with programmatic stream serialisation: this grid may be scheduled while the previous kernel in
+    // the stream is still running, which hides its launch latency on the decode path; it touches memory only after
+    // that kernel has finished, and lets the kernel behind it start its own set-up right away.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const int tid = threadIdx.x;
