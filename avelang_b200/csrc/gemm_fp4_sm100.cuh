@@ -76,6 +76,9 @@ struct GemmParams {
     float* rs_dst[8];
     int rs_rows;               // rows per owner, a multiple of 32
     int rs_world;
+    int pdl;                   // 1: launched with programmatic stream serialisation -- the grid may be scheduled while the
+                               //    previous kernel in the stream still runs; it touches global memory only after that
+                               //    kernel has finished (griddepcontrol.wait), so only launch and set-up are overlapped
 };
 
 // Activations of the fused epilogue, evaluated in fp32 on (scaled accumulator + bias) before the bf16 rounding.
@@ -264,6 +267,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         // The whole warp walks the loop (so loop state is warp-uniform); one elected lane issues.
         {
             const bool issuer = elect_one_sync();
+            if (p.pdl) {
+                if (issuer) pdl_launch_dependents();   // the next kernel may be scheduled as soon as SMs free up
+                pdl_wait_prior_grid();                 // operands may come from the previous kernel
+            }
             const uint32_t full0 = (CTA_GROUP == 2) ? mapa_shared(bar_full, 0) : bar_full;
             int stage = 0;
             uint32_t phase = 0;
@@ -414,6 +421,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int half = (warp - 2) >> 2;      // which half of the accumulator columns
         const uint32_t sbuf = smem_base + Cfg::kOffEpi + (warp - 2) * Cfg::kEpiBufBytes;
+        // everything this role reads (tensor scales, bias) or writes may be touched by the previous kernel
+        if (p.pdl) pdl_wait_prior_grid();
         float alpha = 1.0f;
         if (p.a_gs) alpha *= __ldg(p.a_gs);
         if (p.b_gs) alpha *= __ldg(p.b_gs);
