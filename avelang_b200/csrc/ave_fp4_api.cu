@@ -631,15 +631,28 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
     float* gs = static_cast<float*>(global_scale);
     uint8_t* pk = static_cast<uint8_t*>(packed);
     uint8_t* sf = static_cast<uint8_t*>(scales);
-    const unsigned g = static_cast<unsigned>(blocks);
+    // launched with programmatic stream serialisation: the launch overlaps the tail of the previous kernel (the amax
+    // pass, or the GEMM before it); the kernel waits for that kernel on the device before its first access
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    long long rows_ll = rows, k_ll = k, ldx_ll = ldx;
+    const unsigned int* no_amax = nullptr;
+    float* no_gs = nullptr;
     if (fmt == AVE_FP4_FMT_NVFP4) {
-        if (tiled) quantize_fp4_kernel<kFmtNvfp4, true><<<g, 256, 0, s>>>(x, rows, k, ldx, amax, gs, pk, sf);
-        else quantize_fp4_kernel<kFmtNvfp4, false><<<g, 256, 0, s>>>(x, rows, k, ldx, amax, gs, pk, sf);
+        if (tiled) AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_fp4_kernel<kFmtNvfp4, true>, x, rows_ll, k_ll, ldx_ll, amax, gs, pk, sf));
+        else AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_fp4_kernel<kFmtNvfp4, false>, x, rows_ll, k_ll, ldx_ll, amax, gs, pk, sf));
     } else {
-        if (tiled) quantize_fp4_kernel<kFmtMxfp4, true><<<g, 256, 0, s>>>(x, rows, k, ldx, nullptr, nullptr, pk, sf);
-        else quantize_fp4_kernel<kFmtMxfp4, false><<<g, 256, 0, s>>>(x, rows, k, ldx, nullptr, nullptr, pk, sf);
+        if (tiled) AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_fp4_kernel<kFmtMxfp4, true>, x, rows_ll, k_ll, ldx_ll, no_amax, no_gs, pk, sf));
+        else AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_fp4_kernel<kFmtMxfp4, false>, x, rows_ll, k_ll, ldx_ll, no_amax, no_gs, pk, sf));
     }
-    AVE_CUDA(cudaGetLastError());
     return 0;
 }
 

@@ -287,8 +287,10 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
                     const unsigned int* __restrict__ amax_bits, float* __restrict__ gs_io,
                     uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
     // a kernel queued behind this one with programmatic stream serialisation may start its prologue now
-    // (it still waits for this grid to finish before it reads what is written here)
+    // (it still waits for this grid to finish before it reads what is written here); this kernel is launched
+    // the same way and waits for its own predecessor before it touches memory
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long warp_global = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
     const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
     float gs = 1.0f;
