@@ -315,10 +315,11 @@ int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, i
     return 0;
 }
 
-// Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit);
+// Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit) when the
+// ring holds two such bursts, otherwise half the ring, so that one burst can be refilled while the other is consumed;
 // AVE_FP4_SKINNY_BURST overrides it for tuning.
 int skinny_burst(int stages) {
-    int b = 4;
+    int b = stages >= 8 ? 4 : stages / 2;
     if (const char* e = getenv("AVE_FP4_SKINNY_BURST")) b = atoi(e);
     const int cap = stages < 8 ? stages : 8;
     if (b < 1) b = 1;

@@ -10,6 +10,7 @@ Files written next to this script:
   known_answers.json   element / scale rounding at every threshold and tie, saturation, subnormals
   small_cases.npz      tiny end-to-end cases with stored inputs (one-hot, outlier channel, heavy tail, zeros)
   c0_nvfp4.npz         the 128x256x512 NVFP4 case with seed-0 inputs: quantised operands and bf16 result
+  c0_epilogue.npz      the same case through the fused epilogues: bias, act(x + bias) as bf16, and the result quantised to NVFP4
 """
 import hashlib
 import json
@@ -130,12 +131,39 @@ def c0_case() -> dict:
     }
 
 
+def epilogue_case(c0: dict) -> dict:
+    """Fused-epilogue expectations on the C0 operands: the C restatement, cross-checked against the numpy one."""
+    qa = (c0["a_packed"], c0["a_scales"], float(c0["a_gs"]))
+    qb = (c0["b_packed"], c0["b_scales"], float(c0["b_gs"]))
+    d32, _ = O.c_gemm_fp4(qa, qb, O.NVFP4)
+    n = d32.shape[1]
+    bias = bits_of((inputs.normal_bf16(1, n, seed=2).float() * float(np.abs(d32).mean())).to(torch.bfloat16).reshape(n))
+    out = {"bias": bias}
+    for name, act, use_bias in (("bias_gelu", O.ACT_GELU, True), ("bias_silu", O.ACT_SILU, True), ("relu", O.ACT_RELU, False),
+                                ("bias_gelu_tanh", O.ACT_GELU_TANH, True)):
+        y32, ybf = O.c_bias_act(d32, bias if use_bias else None, act)
+        n32, nbf = O.np_bias_act(d32, bias if use_bias else None, act)
+        assert np.allclose(y32, n32, rtol=3e-7, atol=1e-9), name
+        assert ((ybf != nbf) & (np.abs(y32) > 1e-6)).mean() < 1e-3, name
+        out["d_" + name] = ybf
+    # the quantising epilogue: bias + gelu, bf16, then NVFP4 with a static tensor scale (amax / 2688 of that result)
+    ybf = out["d_bias_gelu"]
+    gs = O.c_global_scale(O.c_amax(ybf))
+    qp, qs, qg = O.c_quantize(ybf, O.NVFP4, gs)
+    np_p, np_s, _ = O.np_quantize(ybf, O.NVFP4, gs)
+    assert np.array_equal(qp, np_p) and np.array_equal(qs, np_s)
+    out.update({"q_gs": np.float32(qg), "q_packed": qp, "q_scales": qs})
+    return out
+
+
 def main() -> None:
     with open(os.path.join(HERE, "known_answers.json"), "w") as f:
         json.dump(known_answers(), f, indent=1)
     np.savez_compressed(os.path.join(HERE, "small_cases.npz"), **small_cases())
-    np.savez_compressed(os.path.join(HERE, "c0_nvfp4.npz"), **c0_case())
-    for fn in ("known_answers.json", "small_cases.npz", "c0_nvfp4.npz"):
+    c0 = c0_case()
+    np.savez_compressed(os.path.join(HERE, "c0_nvfp4.npz"), **c0)
+    np.savez_compressed(os.path.join(HERE, "c0_epilogue.npz"), **epilogue_case(c0))
+    for fn in ("known_answers.json", "small_cases.npz", "c0_nvfp4.npz", "c0_epilogue.npz"):
         print(fn, os.path.getsize(os.path.join(HERE, fn)), "bytes")
 
 

@@ -180,3 +180,26 @@ def test_epilogues_inside_cuda_graph(cuda_device):
     ave.check_device_status(cuda_device)
     assert torch.equal(out, ref)
     assert torch.equal(q.packed, qref.packed) and torch.equal(q.scales, qref.scales)
+
+
+def test_epilogue_golden_fixture(cuda_device, oracle):
+    """The kernels against the committed fused-epilogue fixture on the C0 operands (tests/golden/c0_epilogue.npz)."""
+    import os
+
+    from conftest import GOLDEN
+
+    z = np.load(os.path.join(GOLDEN, "c0_nvfp4.npz"))
+    e = np.load(os.path.join(GOLDEN, "c0_epilogue.npz"))
+    A = _to_dev((z["a_packed"], z["a_scales"], float(z["a_gs"])), ave.NVFP4, cuda_device)
+    B = _to_dev((z["b_packed"], z["b_scales"], float(z["b_gs"])), ave.NVFP4, cuda_device)
+    bias = torch.from_numpy(e["bias"].view(np.int16)).view(torch.bfloat16).to(cuda_device)
+    for name, act, use_bias in (("bias_gelu", "gelu", True), ("bias_silu", "silu", True), ("relu", "relu", False),
+                                ("bias_gelu_tanh", "gelu_tanh", True)):
+        for variant in (ave.GEMM_2CTA_N256, ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N192):
+            out = ave.gemm_nvfp4_transposed_b(A, B, variant=variant, bias=bias if use_bias else None, activation=act)
+            _check(out, e["d_" + name], oracle, f"golden {name} variant {variant}")
+    gs = torch.tensor([e["q_gs"]], dtype=torch.float32, device=cuda_device)
+    q = ave.gemm_quantized_out_transposed_b(A, B, gs, bias=bias, activation="gelu", sf_layout=ave.SF_ROW_MAJOR)
+    ave.check_device_status(cuda_device)
+    assert (q.packed.cpu().numpy() != e["q_packed"]).mean() < 5e-3
+    assert (q.scales.cpu().numpy() != e["q_scales"]).mean() < 2e-3

@@ -215,3 +215,20 @@ def test_bias_act_c_matches_numpy(oracle, act):
                 3: [0.841192, -0.158808, 0.0], 4: [0.7310586, -0.26894143, 0.0]}[act]
     y, _ = oracle.c_bias_act(one, None, act)
     assert np.allclose(y[0], expected, rtol=1e-6, atol=1e-7)
+
+
+def test_epilogue_golden_reproduced(oracle):
+    """The committed fused-epilogue fixture (C0 operands): the oracle reproduces every expected array, and the
+    numpy restatement of the quantise step agrees on the quantised result."""
+    z = np.load(os.path.join(GOLDEN, "c0_nvfp4.npz"))
+    e = np.load(os.path.join(GOLDEN, "c0_epilogue.npz"))
+    qa = (z["a_packed"], z["a_scales"], float(z["a_gs"]))
+    qb = (z["b_packed"], z["b_scales"], float(z["b_gs"]))
+    d32, _ = oracle.c_gemm_fp4(qa, qb, oracle.NVFP4)
+    for name, act, use_bias in (("bias_gelu", 2, True), ("bias_silu", 4, True), ("relu", 1, False), ("bias_gelu_tanh", 3, True)):
+        _, ybf = oracle.c_bias_act(d32, e["bias"] if use_bias else None, act)
+        assert np.array_equal(ybf, e["d_" + name]), name
+    qp, qs, qg = oracle.c_quantize(e["d_bias_gelu"], oracle.NVFP4, float(e["q_gs"]))
+    assert np.array_equal(qp, e["q_packed"]) and np.array_equal(qs, e["q_scales"]) and np.float32(qg) == e["q_gs"]
+    n_p, n_s, _ = oracle.np_quantize(e["d_bias_gelu"], oracle.NVFP4, float(e["q_gs"]))
+    assert np.array_equal(n_p, e["q_packed"]) and np.array_equal(n_s, e["q_scales"])
