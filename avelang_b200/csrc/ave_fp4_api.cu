@@ -315,11 +315,10 @@ int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, i
     return 0;
 }
 
-// Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit) when the
-// ring holds two such bursts, otherwise half the ring, so that one burst can be refilled while the other is consumed;
-// AVE_FP4_SKINNY_BURST overrides it for tuning.
+// Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit), also with
+// the 7-stage ring of the 64-row form (27.0 us with 4, 27.8 with 3 at 64 x 28672 x 8192); AVE_FP4_SKINNY_BURST overrides it.
 int skinny_burst(int stages) {
-    int b = stages >= 8 ? 4 : stages / 2;
+    int b = 4;
     if (const char* e = getenv("AVE_FP4_SKINNY_BURST")) b = atoi(e);
     const int cap = stages < 8 ? stages : 8;
     if (b < 1) b = 1;

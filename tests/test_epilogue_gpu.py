@@ -192,13 +192,13 @@ def test_epilogue_golden_fixture(cuda_device, oracle):
     e = np.load(os.path.join(GOLDEN, "c0_epilogue.npz"))
     A = _to_dev((z["a_packed"], z["a_scales"], float(z["a_gs"])), ave.NVFP4, cuda_device)
     B = _to_dev((z["b_packed"], z["b_scales"], float(z["b_gs"])), ave.NVFP4, cuda_device)
-    bias = torch.from_numpy(e["bias"].view(np.int16)).view(torch.bfloat16).to(cuda_device)
+    bias = torch.from_numpy(e["bias"].astype(np.int16)).view(torch.bfloat16).to(cuda_device)
     for name, act, use_bias in (("bias_gelu", "gelu", True), ("bias_silu", "silu", True), ("relu", "relu", False),
                                 ("bias_gelu_tanh", "gelu_tanh", True)):
         for variant in (ave.GEMM_2CTA_N256, ave.GEMM_1CTA_N128, ave.GEMM_2CTA_N192):
             out = ave.gemm_nvfp4_transposed_b(A, B, variant=variant, bias=bias if use_bias else None, activation=act)
             _check(out, e["d_" + name], oracle, f"golden {name} variant {variant}")
-    gs = torch.tensor([e["q_gs"]], dtype=torch.float32, device=cuda_device)
+    gs = torch.tensor([float(e["q_gs"])], dtype=torch.float32, device=cuda_device)
     q = ave.gemm_quantized_out_transposed_b(A, B, gs, bias=bias, activation="gelu", sf_layout=ave.SF_ROW_MAJOR)
     ave.check_device_status(cuda_device)
     assert (q.packed.cpu().numpy() != e["q_packed"]).mean() < 5e-3
