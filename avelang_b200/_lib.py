@@ -64,7 +64,7 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_gemm_epilogue.restype = i32
         L.ave_fp4_gemm_epilogue.argtypes = L.ave_fp4_gemm.argtypes + [ctypes.POINTER(Epilogue)]
         L.ave_fp4_gemm_partials.restype = i32
-        L.ave_fp4_gemm_partials.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i32, vp]
+        L.ave_fp4_gemm_partials.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i32, i64, i64, i64, i32, vp]
         L.ave_fp4_reduce_partials.restype = i32
         L.ave_fp4_reduce_partials.argtypes = [vp, i32, i64, i64, vp, i64, ctypes.POINTER(Epilogue), vp]
         L.ave_fp4_check.restype = i32

@@ -195,7 +195,7 @@ template <int CG, int BN, int VEC, int ST, int ACC>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
                 void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr,
-                void* const* slabs = nullptr, int rs_world = 0) {
+                void* const* slabs = nullptr, int rs_world = 0, int first_owner = 0) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
@@ -231,6 +231,8 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.rs_world = rs_world;
     p.rs_rows = rs_world > 0 ? static_cast<int>(m / rs_world) : 0;
     for (int i = 0; i < 8; ++i) p.rs_dst[i] = (i < rs_world) ? static_cast<float*>(slabs[i]) : nullptr;
+    // K-sharded partials: start the schedule at the tile row that holds first_owner's first row
+    p.tm_rotate = rs_world > 0 ? static_cast<int>((static_cast<int64_t>(first_owner) * p.rs_rows / (128 * CG)) % p.tiles_m) : 0;
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
@@ -742,7 +744,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
                       const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                       int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
                       void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr, void* const* slabs = nullptr,
-                      int rs_world = 0) {
+                      int rs_world = 0, int first_owner = 0) {
     DeviceState* ds = nullptr;
     int rc = current_state(&ds);
     if (rc) return rc;
@@ -778,7 +780,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
         v = AVE_FP4_GEMM_1CTA_N128;   // the quantising epilogue lives in the tiled kernels
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
-#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi, slabs, rs_world
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi, slabs, rs_world, first_owner
     switch (v) {
         case AVE_FP4_GEMM_1CTA_N128:
             return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
@@ -843,8 +845,9 @@ int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void
 }
 
 int ave_fp4_gemm_partials(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
-                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int64_t m,
-                          int64_t n, int64_t k, int fmt, void* stream) {
+                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int first_owner,
+                          int64_t m, int64_t n, int64_t k, int fmt, void* stream) {
+    if (first_owner < 0 || first_owner >= world) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: first_owner %d out of range", first_owner);
     if (world < 1 || world > 8) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: world must be 1..8, got %d", world);
     if (slab_dst == nullptr) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: slab_dst is NULL");
     if (m <= 0 || m % (static_cast<int64_t>(world) * 32) != 0)
@@ -852,7 +855,7 @@ int ave_fp4_gemm_partials(const void* a_packed, const void* a_scales, const void
     for (int i = 0; i < world; ++i)
         if (!slab_dst[i] || !aligned16(slab_dst[i])) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_partials: slab pointer %d is null or misaligned", i);
     return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, nullptr, m, n, k, n, fmt,
-                      AVE_FP4_GEMM_2CTA_N256, nullptr, 0, stream, nullptr, 0, nullptr, slab_dst, world);
+                      AVE_FP4_GEMM_2CTA_N256, nullptr, 0, stream, nullptr, 0, nullptr, slab_dst, world, first_owner);
 }
 
 int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int64_t n, void* d_bf16, int64_t ldd,

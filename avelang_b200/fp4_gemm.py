@@ -387,10 +387,12 @@ def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor,
     return _gemm(A, B, out, A.fmt, variant, peer_ptrs)
 
 
-def gemm_partials_transposed_b(A: Fp4Operand, B: Fp4Operand, slab_ptrs: list[int]) -> None:
+def gemm_partials_transposed_b(A: Fp4Operand, B: Fp4Operand, slab_ptrs: list[int], first_owner: int = 0) -> None:
     """First half of a K-sharded GEMM + reduce-scatter.  A (M, K_r) and B (N, K_r) are this rank's K-slices; the
     fp32 product is scattered by rows: rows ``[j*M/w, (j+1)*M/w)`` are stored (row stride N) at ``slab_ptrs[j]``,
-    raw device addresses valid on this GPU (peer-mapped for other ranks' buffers), ``w = len(slab_ptrs)``."""
+    raw device addresses valid on this GPU (peer-mapped for other ranks' buffers), ``w = len(slab_ptrs)``.  The tile
+    schedule starts at the rows of owner ``first_owner``; ranks should pass different values (rank + 1 mod w) so that
+    their stores are spread over all destination GPUs at any time."""
     fmt = A.fmt
     if B.fmt != fmt:
         raise ValueError("A and B must have the same format.")
@@ -400,6 +402,8 @@ def gemm_partials_transposed_b(A: Fp4Operand, B: Fp4Operand, slab_ptrs: list[int
         raise ValueError(f"A and B must share K, got {k} and {B.k}.")
     if not 1 <= world <= 8:
         raise ValueError(f"1..8 slabs, got {world}.")
+    if not 0 <= first_owner < world:
+        raise ValueError(f"first_owner must be in [0, {world}), got {first_owner}.")
     if m <= 0 or m % (32 * world) != 0:
         raise ValueError(f"M must be a positive multiple of 32 * world = {32 * world}, got {m}.")
     if n % 8 != 0 or k % 32 != 0 or k == 0:
@@ -417,7 +421,7 @@ def gemm_partials_transposed_b(A: Fp4Operand, B: Fp4Operand, slab_ptrs: list[int
         L = _lib.ensure_init(dev)
         arr = (ctypes.c_void_p * world)(*slab_ptrs)
         _lib.check(L.ave_fp4_gemm_partials(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed), _ptr(B.scales),
-                                           _ptr(B.global_scale), arr, world, m, n, k, fmt, _stream(A.device)))
+                                           _ptr(B.global_scale), arr, world, first_owner, m, n, k, fmt, _stream(A.device)))
 
 
 def reduce_partials(slabs: torch.Tensor, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,

@@ -194,10 +194,10 @@ class RowShardedFp4Linear:
         self._buffers(m, n, x_kshard.device)
         if self.fused:
             self._hdl.barrier()      # every rank has finished reading its staging buffer from the previous step
-            gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs)
+            gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs, first_owner=(self.rank + 1) % self.world)
             self._hdl.barrier()      # every rank's partials have landed
             return reduce_partials(self._staging, out=out, bias=bias, activation=activation)
-        gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs)
+        gemm_partials_transposed_b(x_kshard, self.weight, self._ptrs, first_owner=(self.rank + 1) % self.world)
         if self.world > 1:
             dist.reduce_scatter_tensor(self._sum[0], self._staging.view(-1, n), op=dist.ReduceOp.SUM, group=self.group)
             return reduce_partials(self._sum, out=out, bias=bias, activation=activation)

@@ -213,15 +213,17 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
  * (tensor scales applied, no rounding) is scattered by the epilogue's own stores: rows [j*m/world, (j+1)*m/world)
  * go, row stride n, to slab_dst[j] -- a device pointer valid on THIS GPU to the (m/world, n) fp32 slab this rank owns
  * inside rank j's staging buffer (peer-mapped memory for j != this rank, plain stores over NVLink; `slab_dst` is a host
- * array read during the call).  m % (32 * world) == 0; 256x256 CTA-pair tiles.
+ * array read during the call).  m % (32 * world) == 0; 256x256 CTA-pair tiles.  The tile schedule starts at the rows of
+ * owner `first_owner` and wraps around: give every rank a different one (e.g. rank + 1 mod world), otherwise all ranks
+ * store to the same destination GPU at the same time and its NVLink ingress, not the senders' egress, sets the pace.
  *
  * ave_fp4_reduce_partials: after every rank's partials have landed (the caller synchronises the ranks), the owner sums
  * its `world` slabs (fp32 (rows, n), back to back, in slab order -- deterministic), applies the optional bias and
  * activation, and rounds to bf16 once.
  */
 int ave_fp4_gemm_partials(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
-                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int64_t m,
-                          int64_t n, int64_t k, int fmt, void* stream);
+                          const void* b_scales, const void* b_global_scale, void* const* slab_dst, int world, int first_owner,
+                          int64_t m, int64_t n, int64_t k, int fmt, void* stream);
 int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int64_t n, void* d_bf16, int64_t ldd,
                             const ave_fp4_epilogue* epilogue, void* stream);
 

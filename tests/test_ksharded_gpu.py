@@ -39,7 +39,7 @@ def test_emulated_ranks_match_oracle(cuda_device, oracle, fmt, world, m, n, k):
         deq_w.append(oracle.c_dequantize(*qw, fmt))
         offs = sharded.slab_offsets(world, r, rows, n)
         ptrs = [staging[j].data_ptr() + offs[j] for j in range(world)]
-        fp4_gemm.gemm_partials_transposed_b(_to_dev(qa, fmt, dev), _to_dev(qw, fmt, dev), ptrs)
+        fp4_gemm.gemm_partials_transposed_b(_to_dev(qa, fmt, dev), _to_dev(qw, fmt, dev), ptrs, first_owner=(r + 1) % world)
     bias = (inputs.normal_bf16(1, n, 5).float() * 0.1).to(torch.bfloat16).reshape(n)
     outs = [fp4_gemm.reduce_partials(staging[j], bias=bias.to(dev), activation="relu") for j in range(world)]
     ave.check_device_status(dev)
