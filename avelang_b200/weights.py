@@ -1,4 +1,4 @@
-"""On-disk format for pre-quantised FP4 weights, and a loader that shards by output rows (N).
+"""On-disk format for pre-quantised FP4 weights, and a loader that shards by output rows (N) or by K.
 
 Weights are quantised once, offline; serving loads the bytes and never touches bf16 again.  The file
 holds the operand in its layout-neutral form -- packed nibbles (N, K/2), row-major scale bytes
@@ -27,7 +27,7 @@ import numpy as np
 import torch
 
 from .fp4_gemm import MXFP4, NVFP4, SF_ROW_MAJOR, Fp4Operand, make_operand, pack_weight_tiles, to_tiled
-from .sharded import shard_bounds
+from .sharded import k_shard_bounds, shard_bounds
 
 MAGIC = b"AVEFP4W1"
 _ALIGN = 64
@@ -75,30 +75,47 @@ def read_header(path: str) -> dict:
 
 
 def load_fp4_weights(path: str, device: torch.device | str = "cpu", world: int = 1, rank: int = 0,
-                     tile_major: bool = False) -> Fp4Operand:
-    """Read rows [lo, hi) = this rank's N-shard of the weight (the whole matrix for world = 1).
+                     tile_major: bool = False, shard: str = "n") -> Fp4Operand:
+    """Read this rank's shard of the weight (the whole matrix for world = 1).
 
-    Only the shard's bytes are read from the file.  On a CUDA device the scales are converted to the
-    tiled layout the GEMM consumes; `tile_major=True` also re-packs the nibbles for the decode kernel.
-    The tensor scale in the file is the scale of the whole matrix, so every shard dequantises exactly
-    as the unsharded weight does.
+    shard="n": rows [lo, hi) -- the column-parallel layer (`ShardedFp4Linear`); only the shard's bytes are read, one
+    contiguous range per section.  shard="k": the K-elements [lo, hi) of every row -- the row-parallel layer
+    (`RowShardedFp4Linear`); one strided read per section (memory-mapped, so again only the shard's bytes are touched).
+    On a CUDA device the scales are converted to the tiled layout the GEMM consumes; `tile_major=True` also re-packs the
+    nibbles for the decode kernel.  The tensor scale in the file is the scale of the whole matrix, so every shard
+    dequantises exactly as the unsharded weight does.
     """
     h = read_header(path)
     fmt = NVFP4 if h["fmt"] == "nvfp4" else MXFP4
     rows, k, block = int(h["rows"]), int(h["k"]), int(h["block"])
-    lo, hi = (0, rows) if world == 1 else shard_bounds(rows, world, rank)
-    n = hi - lo
-    packed = np.fromfile(path, dtype=np.uint8, count=n * (k // 2), offset=h["packed_offset"] + lo * (k // 2))
-    scales = np.fromfile(path, dtype=np.uint8, count=n * (k // block), offset=h["scales_offset"] + lo * (k // block))
-    if packed.size != n * (k // 2) or scales.size != n * (k // block):
-        raise ValueError(f"{path} is truncated.")
+    if shard not in ("n", "k"):
+        raise ValueError(f"shard must be 'n' or 'k', got {shard!r}.")
+    if shard == "n":
+        lo, hi = (0, rows) if world == 1 else shard_bounds(rows, world, rank)
+        n, kk = hi - lo, k
+        packed = np.fromfile(path, dtype=np.uint8, count=n * (k // 2), offset=h["packed_offset"] + lo * (k // 2))
+        scales = np.fromfile(path, dtype=np.uint8, count=n * (k // block), offset=h["scales_offset"] + lo * (k // block))
+        if packed.size != n * (k // 2) or scales.size != n * (k // block):
+            raise ValueError(f"{path} is truncated.")
+        packed, scales = packed.reshape(n, k // 2), scales.reshape(n, k // block)
+    else:
+        lo, hi = (0, k) if world == 1 else k_shard_bounds(k, world, rank)
+        n, kk = rows, hi - lo
+        try:
+            pm = np.memmap(path, dtype=np.uint8, mode="r", offset=h["packed_offset"], shape=(rows, k // 2))
+            sm = np.memmap(path, dtype=np.uint8, mode="r", offset=h["scales_offset"], shape=(rows, k // block))
+        except ValueError as exc:
+            raise ValueError(f"{path} is truncated.") from exc
+        packed = np.ascontiguousarray(pm[:, lo // 2:hi // 2])
+        scales = np.ascontiguousarray(sm[:, lo // block:hi // block])
     device = torch.device(device)
-    p = torch.from_numpy(packed.reshape(n, k // 2)).to(device)
-    s = torch.from_numpy(scales.reshape(n, k // block)).to(device)
+    p = torch.from_numpy(packed).to(device)
+    s = torch.from_numpy(scales).to(device)
     gs = None
     if fmt == NVFP4:
         gs = torch.tensor([h["global_scale"]], dtype=torch.float32, device=device)
     op = make_operand(p, s, gs, fmt, SF_ROW_MAJOR)
+    assert op.rows == n and op.k == kk
     if device.type == "cuda":
         op = pack_weight_tiles(op) if tile_major else to_tiled(op)
     return op
