@@ -106,8 +106,8 @@ def load_fp4_weights(path: str, device: torch.device | str = "cpu", world: int =
             sm = np.memmap(path, dtype=np.uint8, mode="r", offset=h["scales_offset"], shape=(rows, k // block))
         except ValueError as exc:
             raise ValueError(f"{path} is truncated.") from exc
-        packed = np.ascontiguousarray(pm[:, lo // 2:hi // 2])
-        scales = np.ascontiguousarray(sm[:, lo // block:hi // block])
+        packed = np.array(pm[:, lo // 2:hi // 2], order="C", copy=True)
+        scales = np.array(sm[:, lo // block:hi // block], order="C", copy=True)
     device = torch.device(device)
     p = torch.from_numpy(packed).to(device)
     s = torch.from_numpy(scales).to(device)
