@@ -231,8 +231,18 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.rs_world = rs_world;
     p.rs_rows = rs_world > 0 ? static_cast<int>(m / rs_world) : 0;
     for (int i = 0; i < 8; ++i) p.rs_dst[i] = (i < rs_world) ? static_cast<float*>(slabs[i]) : nullptr;
-    // K-sharded partials: start the schedule at the tile row that holds first_owner's first row
-    p.tm_rotate = rs_world > 0 ? static_cast<int>((static_cast<int64_t>(first_owner) * p.rs_rows / (128 * CG)) % p.tiles_m) : 0;
+    // K-sharded partials: visit the owners' tile rows in turn, starting with first_owner; when the owners' row ranges are not
+    // whole tile rows, only start the schedule at the tile row that holds first_owner's first row
+    p.tm_perm_w = 0;
+    p.tm_first = 0;
+    if (rs_world > 1) {
+        if (p.tiles_m % rs_world == 0 && p.rs_rows % (128 * CG) == 0) {
+            p.tm_perm_w = rs_world;
+            p.tm_first = first_owner;
+        } else {
+            p.tm_first = static_cast<int>((static_cast<int64_t>(first_owner) * p.rs_rows / (128 * CG)) % p.tiles_m);
+        }
+    }
 
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;

@@ -76,7 +76,8 @@ struct GemmParams {
     float* rs_dst[8];
     int rs_rows;               // rows per owner, a multiple of 32
     int rs_world;
-    int tm_rotate;             // cyclic shift of the tile rows in the schedule, 0 <= tm_rotate < tiles_m
+    int tm_perm_w;             // tile-row order of the schedule, see decode_tile: owners visited in turn (0 = off)
+    int tm_first;              // first owner (tm_perm_w > 0) or cyclic shift of the tile rows (tm_perm_w = 0)
     int pdl;                   // 1: launched with programmatic stream serialisation -- the grid may be scheduled while the
                                //    previous kernel in the stream still runs; it touches global memory only after that
                                //    kernel has finished (griddepcontrol.wait), so only launch and set-up are overlapped
@@ -189,17 +190,28 @@ struct GemmConfig {
 
 // Tile index -> (tile_m, tile_n): bands of 8 tile rows, M fastest inside a band, so
 // concurrently running CTAs share a few A panels and a few B panels in L2.
-// `rotate` shifts the tile rows cyclically (tile row 0 is visited as row `rotate`): the ranks of a K-sharded GEMM
-// start at different owners' rows, so that their scattered stores do not all converge on one GPU at a time.
-__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int rotate, int& tm, int& tn) {
+// K-sharded GEMMs scatter their tile rows to different owner GPUs, so the order of the tile rows decides where the
+// stores go at any moment.  With `perm_w` owners of tiles_m / perm_w tile rows each, consecutive positions of the schedule
+// visit the owners in turn, starting with owner `first` (position p -> owner (first + p mod w) mod w, its row p / w): every
+// rank sends to every owner all the time, NVLink traffic is spread over the whole kernel and no GPU's ingress is the target
+// of all ranks at once.  perm_w = 0: tile rows are only shifted cyclically by `first` (0 = the plain order).
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int perm_w, int first, int& tm, int& tn) {
     constexpr int kGroup = 8;
     const int band = kGroup * tiles_n;
     const int g = t / band;
-    const int first = g * kGroup;
-    const int gm = min(tiles_m - first, kGroup);
+    const int first_row = g * kGroup;
+    const int gm = min(tiles_m - first_row, kGroup);
     const int r = t - g * band;
-    tm = first + r % gm + rotate;
-    if (tm >= tiles_m) tm -= tiles_m;
+    const int pos = first_row + r % gm;
+    if (perm_w > 0) {
+        const int per_owner = tiles_m / perm_w;
+        int owner = first + pos % perm_w;
+        if (owner >= perm_w) owner -= perm_w;
+        tm = owner * per_owner + pos / perm_w;
+    } else {
+        tm = pos + first;
+        if (tm >= tiles_m) tm -= tiles_m;
+    }
     tn = r / gm;
 }
 
@@ -283,7 +295,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int rec = 0;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 int tm, tn;
-                decode_tile(t, p.tiles_m, p.tiles_n, p.tm_rotate, tm, tn);
+                decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
                 const int row_a = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM;
                 const int row_b = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBnCta;
                 const int sfa_atom0 = (row_a / 128) * p.sf_k_atoms;
@@ -360,7 +372,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 uint32_t sfb_shift = 0;
                 if constexpr (BLOCK_N % 128 != 0) {
                     int tm, tn;
-                    decode_tile(t, p.tiles_m, p.tiles_n, p.tm_rotate, tm, tn);
+                    decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
                     sfb_shift = static_cast<uint32_t>(((tn * BLOCK_N) % 128) / 32);
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -442,7 +454,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         int tile_iter = 0;
         for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
             int tm, tn;
-            decode_tile(t, p.tiles_m, p.tiles_n, p.tm_rotate, tm, tn);
+            decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
             const int acc = tile_iter % ACC_STAGES;
             const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
             const bool tr = (p.trace != nullptr) && (blockIdx.x == 0) && (warp == 2) && (lane == 0) && (tile_iter < p.trace_cap);

@@ -213,9 +213,9 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
  * (tensor scales applied, no rounding) is scattered by the epilogue's own stores: rows [j*m/world, (j+1)*m/world)
  * go, row stride n, to slab_dst[j] -- a device pointer valid on THIS GPU to the (m/world, n) fp32 slab this rank owns
  * inside rank j's staging buffer (peer-mapped memory for j != this rank, plain stores over NVLink; `slab_dst` is a host
- * array read during the call).  m % (32 * world) == 0; 256x256 CTA-pair tiles.  The tile schedule starts at the rows of
- * owner `first_owner` and wraps around: give every rank a different one (e.g. rank + 1 mod world), otherwise all ranks
- * store to the same destination GPU at the same time and its NVLink ingress, not the senders' egress, sets the pace.
+ * array read during the call).  m % (32 * world) == 0; 256x256 CTA-pair tiles.  The tile schedule visits the owners' rows
+ * in turn, starting with owner `first_owner`: give every rank a different one (e.g. rank + 1 mod world), so that at any
+ * moment the ranks store to different destination GPUs and no NVLink ingress is the target of all of them.
  *
  * ave_fp4_reduce_partials: after every rank's partials have landed (the caller synchronises the ranks), the owner sums
  * its `world` slabs (fp32 (rows, n), back to back, in slab order -- deterministic), applies the optional bias and
