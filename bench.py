@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 NVLINK_GBS_PER_DIR = 770.0       # measured peer copy per direction on this pool
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (None until a capture of that kernel has been taken)
-NCU_TRAFFIC_BYTES = {"gemm_8192": 245_865_216, "decode": 137_693_000}
+NCU_TRAFFIC_BYTES = {"gemm_8192": 250_128_768, "decode": 137_693_000}
 
 
 def measured_peaks():
