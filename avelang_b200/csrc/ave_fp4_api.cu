@@ -137,30 +137,68 @@ int current_state(DeviceState** out) {
 // Tensor maps.
 // L2 fetch granularity of TMA loads (256 bytes unless AVE_FP4_L2_PROMOTION = 64 | 128 | 0 overrides it for tuning).
 CUtensorMapL2promotion l2_promotion() {
-    if (const char* e = getenv("AVE_FP4_L2_PROMOTION")) {
-        const int v = atoi(e);
-        if (v == 0) return CU_TENSOR_MAP_L2_PROMOTION_NONE;
-        if (v == 64) return CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
-        if (v == 128) return CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-    }
-    return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    static const CUtensorMapL2promotion chosen = [] {
+        if (const char* e = getenv("AVE_FP4_L2_PROMOTION")) {
+            const int v = atoi(e);
+            if (v == 0) return CU_TENSOR_MAP_L2_PROMOTION_NONE;
+            if (v == 64) return CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
+            if (v == 128) return CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+        }
+        return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    }();
+    return chosen;
 }
+
+// A tensor map depends only on the address and the geometry, never on the memory's contents, and a serving loop
+// calls with the same few operands over and over (the weights of each layer, a handful of activation buffers).
+// Each host thread therefore keeps the maps it encoded last in a small direct-mapped cache: a hit replaces the
+// driver call (four per GEMM launch) by a 128-byte copy.
+struct TensorMapKey {
+    const void* base;
+    uint64_t inner, outer, stride;
+    uint32_t box_inner, box_outer;
+    int dt, swz, promo;
+    bool operator==(const TensorMapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+               box_outer == o.box_outer && dt == o.dt && swz == o.swz && promo == o.promo;
+    }
+};
+struct TensorMapSlot {
+    bool valid = false;
+    TensorMapKey key{};
+    CUtensorMap map;
+};
+constexpr int kTensorMapSlots = 256;
+thread_local TensorMapSlot g_tm_cache[kTensorMapSlots];
 
 int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
               uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
               const char* what) {
+    const CUtensorMapL2promotion promo = l2_promotion();
+    const TensorMapKey key{base, inner, outer, outer_stride_bytes, box_inner, box_outer, static_cast<int>(dt),
+                           static_cast<int>(swz), static_cast<int>(promo)};
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h = (h ^ (h >> 17) ^ (outer * 0x9E3779B97F4A7C15ull) ^ (static_cast<uint64_t>(box_outer) << 7) ^ inner) * 0xD6E8FEB86659FD93ull;
+    TensorMapSlot& slot = g_tm_cache[(h >> 40) % kTensorMapSlots];
+    if (slot.valid && slot.key == key) {
+        memcpy(tm, &slot.map, sizeof(CUtensorMap));
+        return 0;
+    }
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {outer_stride_bytes};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swz, l2_promotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swz, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(-AVE_FP4_ERR_ARG,
                     "tensor map for %s rejected (CUresult %d): base %p dims (%llu,%llu) stride %llu box (%u,%u)", what,
                     static_cast<int>(r), base, static_cast<unsigned long long>(inner),
                     static_cast<unsigned long long>(outer), static_cast<unsigned long long>(outer_stride_bytes),
                     box_inner, box_outer);
+    slot.key = key;
+    memcpy(&slot.map, tm, sizeof(CUtensorMap));
+    slot.valid = true;
     return 0;
 }
 
@@ -330,8 +368,8 @@ int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, i
 // Load-burst size of the decode kernel: 4 K blocks (512 contiguous bytes per weight row and DRAM page visit), also with
 // the 7-stage ring of the 64-row form (27.0 us with 4, 27.8 with 3 at 64 x 28672 x 8192); AVE_FP4_SKINNY_BURST overrides it.
 int skinny_burst(int stages) {
-    int b = 4;
-    if (const char* e = getenv("AVE_FP4_SKINNY_BURST")) b = atoi(e);
+    static const int env_burst = [] { const char* e = getenv("AVE_FP4_SKINNY_BURST"); return e ? atoi(e) : 4; }();
+    int b = env_burst;
     const int cap = stages < 8 ? stages : 8;
     if (b < 1) b = 1;
     if (b > cap) b = cap;
@@ -500,7 +538,8 @@ extern "C" int ave_fp4_gemm_decode_noalloc(const void* a_packed, const void* a_s
     if (m == 0 || n == 0) return 0;
     if (k <= 0 || k % 32 != 0 || k > 0x7fffffff)
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
-    if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: ldd must be >= N and a multiple of 8");
+    if (n % 8 != 0 || ldd < n || ldd % 8 != 0)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: N and ldd must be multiples of 8 and ldd >= N");
     if (!a_packed || !a_scales || !b_packed || !b_scales || !d_bf16 || !aligned16(a_packed) || !aligned16(a_scales) ||
         !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_decode_noalloc: null or misaligned (16-byte) pointer");
@@ -529,29 +568,35 @@ int ave_fp4_init(int device) {
     if (g_dev[device].ready) return 0;
     int prev = -1;
     AVE_CUDA(cudaGetDevice(&prev));
+    // whatever happens below, the caller gets its current device back, and a status word that was
+    // allocated but not handed over is freed
+    struct Restore {
+        int prev;
+        int* status;
+        ~Restore() {
+            if (status != nullptr) cudaFree(status);
+            cudaSetDevice(prev);
+        }
+    } restore{prev, nullptr};
     AVE_CUDA(cudaSetDevice(device));
     cudaDeviceProp prop;
     AVE_CUDA(cudaGetDeviceProperties(&prop, device));
-    if (prop.major != 10) {
-        cudaSetDevice(prev);
+    if (prop.major != 10)
         return fail(-AVE_FP4_ERR_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
                     prop.minor);
-    }
     if (g_encode == nullptr) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
         AVE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-        if (fn == nullptr || q != cudaDriverEntryPointSuccess) {
-            cudaSetDevice(prev);
+        if (fn == nullptr || q != cudaDriverEntryPointSuccess)
             return fail(-AVE_FP4_ERR_DEVICE, "driver does not export cuTensorMapEncodeTiled");
-        }
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     AVE_CUDA(prepare_all());
-    int* status = nullptr;
-    AVE_CUDA(cudaMalloc(&status, sizeof(int)));
-    AVE_CUDA(cudaMemset(status, 0, sizeof(int)));
-    g_dev[device].status = status;
+    AVE_CUDA(cudaMalloc(&restore.status, sizeof(int)));
+    AVE_CUDA(cudaMemset(restore.status, 0, sizeof(int)));
+    g_dev[device].status = restore.status;
+    restore.status = nullptr;
     g_dev[device].sm_count = prop.multiProcessorCount;
     {
         DeviceState& d = g_dev[device];
@@ -568,7 +613,6 @@ int ave_fp4_init(int device) {
         d.occ_reduce = occ(reduce_partials_kernel);
     }
     g_dev[device].ready = true;
-    AVE_CUDA(cudaSetDevice(prev));
     return 0;
 }
 
@@ -755,14 +799,17 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
                       int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
                       void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr, void* const* slabs = nullptr,
                       int rs_world = 0, int first_owner = 0) {
-    DeviceState* ds = nullptr;
-    int rc = current_state(&ds);
-    if (rc) return rc;
+    // shape and pointer rules first (they need no device), then the per-device state
     if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
     if (m < 0 || n < 0 || k < 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: size out of range");
-    if (m == 0 || n == 0) return 0;
+    if (m == 0 || n == 0) {
+        DeviceState* ds0 = nullptr;
+        return current_state(&ds0);
+    }
     if (k == 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
+    // the write-out moves 16-byte (8-column) chunks and the bias is read the same way
+    if (n % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: N must be a multiple of 8, got %lld", static_cast<long long>(n));
     if (ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: ldd must be >= N and a multiple of 8, got %lld", static_cast<long long>(ldd));
     const bool quant_out = epi && epi->quantize_out;
     if (!a_packed || !a_scales || !b_packed || !b_scales || (!d_bf16 && !quant_out && rs_world == 0) || !aligned16(a_packed) || !aligned16(a_scales) ||
@@ -782,6 +829,9 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
                 return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_epilogue: unknown q_sf_layout %d", epi->q_sf_layout);
         }
     }
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
     const float* ags = static_cast<const float*>(a_global_scale);
     const float* bgs = static_cast<const float*>(b_global_scale);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -8,7 +8,7 @@
 //
 // Work is split so that every SM pulls the same number of bytes, in two phases.  With T weight
 // tiles and G persistent CTAs, the first T mod G tiles are split stream-K style: their (tile, K block)
-// units are cut into G equal contiguous ranges, one per CTA.  A range that covers only part of a
+// units are cut into min(G, units) equal contiguous ranges, one per CTA.  A range that covers only part of a
 // tile's K writes an fp32 partial to scratch memory; the CTA that completes a tile last (per-tile
 // arrival counter) adds the partials in a fixed order and writes the bf16 result, so the output is
 // deterministic and nobody waits on another CTA.  After its range every CTA computes floor(T / G)
@@ -100,8 +100,13 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int whole_tiles = p.tiles_n / static_cast<int>(gridDim.x);            // whole tiles per CTA (second phase)
     const int sk_tiles = p.tiles_n - whole_tiles * static_cast<int>(gridDim.x);  // tiles 0 .. sk_tiles-1 are split stream-K
     const long long units = static_cast<long long>(sk_tiles) * num_kb;           // stream-K units, cut into equal ranges
-    const long long u_begin = (static_cast<long long>(blockIdx.x) * units) / ctas;
-    const long long u_end = (static_cast<long long>(blockIdx.x + 1) * units) / ctas;
+    // Only min(G, units) CTAs take part in the stream-K phase, so that every one of them owns at least one unit:
+    // the finish test below counts one contribution from every CTA between the first and the last owner of a tile.
+    // (With more CTAs than units -- many tiles, short K -- the other CTAs go straight to their whole tiles.)
+    const long long sk_ctas = units < ctas ? units : ctas;
+    const bool in_sk = static_cast<long long>(blockIdx.x) < sk_ctas;
+    const long long u_begin = in_sk ? (static_cast<long long>(blockIdx.x) * units) / sk_ctas : 0;
+    const long long u_end = in_sk ? (static_cast<long long>(blockIdx.x + 1) * units) / sk_ctas : 0;
     const int first_whole = sk_tiles + static_cast<int>(blockIdx.x);              // then tiles first_whole + j * G
 
     const uint32_t bar_full = smem_base + Cfg::kOffBar;
@@ -388,8 +393,8 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                 __syncwarp();
                 int f = -1;
                 if (lane == 0) {
-                    const int c0 = skinny_cta_of(static_cast<long long>(tile) * num_kb, units, ctas);
-                    const int c1 = skinny_cta_of(static_cast<long long>(tile + 1) * num_kb - 1, units, ctas);
+                    const int c0 = skinny_cta_of(static_cast<long long>(tile) * num_kb, units, sk_ctas);
+                    const int c1 = skinny_cta_of(static_cast<long long>(tile + 1) * num_kb - 1, units, sk_ctas);
                     const int old = atomicAdd(p.counters + tile * 4 + quad, 1);
                     if (old == c1 - c0) {
                         p.counters[tile * 4 + quad] = 0;

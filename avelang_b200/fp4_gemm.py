@@ -60,6 +60,7 @@ class Fp4Operand:
     k: int
     sf_layout: int = SF_TILED
     tile_major: bool = False  # packed bytes re-ordered into 16 KB tiles by pack_weight_tiles (decode weights)
+    amax_scratch: torch.Tensor | None = None  # one fp32 on the device, used when the tensor scale is taken from the data
 
     @property
     def shape(self) -> tuple[int, int]:
@@ -93,7 +94,8 @@ def sf_bytes(rows: int, k: int, fmt: int, sf_layout: int) -> int:
     return ((rows + 127) // 128) * ((cols + 3) // 4) * 512
 
 
-def _quantize(x: torch.Tensor, fmt: int, global_scale: torch.Tensor | None, sf_layout: int) -> Fp4Operand:
+def _quantize(x: torch.Tensor, fmt: int, global_scale: torch.Tensor | None, sf_layout: int,
+              out: Fp4Operand | None = None) -> Fp4Operand:
     if x.dtype != torch.bfloat16:
         raise ValueError(f"x must have dtype torch.bfloat16, got {x.dtype}.")
     if x.dim() != 2:
@@ -104,52 +106,77 @@ def _quantize(x: torch.Tensor, fmt: int, global_scale: torch.Tensor | None, sf_l
         raise ValueError(f"K must be a multiple of 32, got {k}.")
     if x.stride(1) != 1 or (rows > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
         raise ValueError("x must be K-contiguous with a 16-byte aligned row stride.")
+    if out is not None:
+        # same convention as the reference operator's `out` (python/avelang_kernels/amdgpu_gemm.py:478-486):
+        # a given result is checked and written in place, nothing is allocated
+        sf_layout = out.sf_layout
+        if out.fmt != fmt or out.shape != (rows, k) or out.tile_major:
+            raise ValueError(f"out must be a {_FMT_NAME[fmt]} operand of shape {(rows, k)}, got {_FMT_NAME.get(out.fmt, out.fmt)} {out.shape}.")
+        if out.device != x.device:
+            raise ValueError(f"out must be on device {x.device}, got {out.device}.")
+        if fmt == NVFP4 and out.global_scale is None:
+            raise ValueError("an NVFP4 out operand needs a global_scale tensor.")
     if sf_layout not in (SF_ROW_MAJOR, SF_TILED):
         raise ValueError(f"unknown scale layout {sf_layout}.")
     ldx = x.stride(0) if rows > 1 else k
     gs = None
     with torch.cuda.device(dev):
         L = _lib.ensure_init(dev)
-        packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
-        if sf_layout == SF_ROW_MAJOR:
-            scales = torch.empty((rows, k // _BLOCK[fmt]), dtype=torch.uint8, device=x.device)
+        if out is not None:
+            packed, scales = out.packed, out.scales
         else:
-            scales = torch.empty((sf_bytes(rows, k, fmt, SF_TILED),), dtype=torch.uint8, device=x.device)
+            packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+            if sf_layout == SF_ROW_MAJOR:
+                scales = torch.empty((rows, k // _BLOCK[fmt]), dtype=torch.uint8, device=x.device)
+            else:
+                scales = torch.empty((sf_bytes(rows, k, fmt, SF_TILED),), dtype=torch.uint8, device=x.device)
         stream = _stream(x.device)
         amax = None
         if fmt == NVFP4:
             if global_scale is None:
                 # tensor scale from the data: one fused launch for small inputs, amax + quantise otherwise
-                both = torch.empty((2,), dtype=torch.float32, device=x.device)
-                gs, amax = both[0:1], both[1:2]
+                if out is not None:
+                    gs = out.global_scale
+                    if out.amax_scratch is None:
+                        out.amax_scratch = torch.empty((1,), dtype=torch.float32, device=x.device)
+                    amax = out.amax_scratch
+                else:
+                    both = torch.empty((2,), dtype=torch.float32, device=x.device)
+                    gs, amax = both[0:1], both[1:2]
                 _lib.check(L.ave_fp4_quantize_nvfp4_dynamic(_ptr(x), rows, k, ldx, _ptr(gs), _ptr(packed), _ptr(scales),
                                                             sf_layout, _ptr(amax), stream))
-                return Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout)
+                return out if out is not None else Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout, False, amax)
             else:
                 if global_scale.dtype != torch.float32 or global_scale.numel() != 1:
                     raise ValueError("global_scale must be a float32 tensor with one element.")
                 if global_scale.device != x.device:
                     raise ValueError(f"global_scale must be on device {x.device}, got {global_scale.device}.")
                 gs = global_scale.reshape(1)
+                if out is not None and out.global_scale.data_ptr() != gs.data_ptr():
+                    out.global_scale.copy_(gs)     # the operand carries its own copy of the static scale
+                    gs = out.global_scale
         elif global_scale is not None:
             raise ValueError("MXFP4 has no global scale.")
         _lib.check(L.ave_fp4_quantize(_ptr(x), rows, k, ldx, fmt, _ptr(amax), _ptr(gs), _ptr(packed), _ptr(scales),
                                       sf_layout, stream))
-    return Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout)
+    return out if out is not None else Fp4Operand(packed, scales, gs, fmt, rows, k, sf_layout)
 
 
-def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor | None = None, sf_layout: int = SF_TILED) -> Fp4Operand:
+def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor | None = None, sf_layout: int = SF_TILED,
+                   out: Fp4Operand | None = None) -> Fp4Operand:
     """bf16 (rows, K) -> NVFP4: 16-element blocks, E4M3 block scales, one fp32 tensor scale.
 
     ``global_scale=None`` computes the tensor scale as amax / (6 * 448) on the device
     (no host synchronisation); a given one-element fp32 tensor is used as a static scale.
+    ``out``: an operand of the same shape (e.g. an earlier result) to overwrite; then nothing is allocated
+    and ``sf_layout`` is taken from it.
     """
-    return _quantize(x, NVFP4, global_scale, sf_layout)
+    return _quantize(x, NVFP4, global_scale, sf_layout, out)
 
 
-def quantize_mxfp4(x: torch.Tensor, sf_layout: int = SF_TILED) -> Fp4Operand:
-    """bf16 (rows, K) -> MXFP4: 32-element blocks, E8M0 (power of two) block scales."""
-    return _quantize(x, MXFP4, None, sf_layout)
+def quantize_mxfp4(x: torch.Tensor, sf_layout: int = SF_TILED, out: Fp4Operand | None = None) -> Fp4Operand:
+    """bf16 (rows, K) -> MXFP4: 32-element blocks, E8M0 (power of two) block scales.  ``out`` as for quantize_nvfp4."""
+    return _quantize(x, MXFP4, None, sf_layout, out)
 
 
 def to_tiled(op: Fp4Operand) -> Fp4Operand:

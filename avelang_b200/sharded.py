@@ -7,7 +7,7 @@ across `world` ranks, rank r computes ``D[:, r*N/w:(r+1)*N/w] = A @ B_r.T`` with
 inter-rank dependency, and the slices are exchanged with one all-gather.
 
 Layout of the gathered result: ``(world, M, N/world)`` -- rank r's column block is the
-contiguous slab ``gathered[r]``; ``columns_view`` presents it as the logical (M, N).
+contiguous slab ``gathered[r]``; ``columns_view`` presents it as a strided (M, world, N/world) view.
 """
 from __future__ import annotations
 
@@ -46,9 +46,10 @@ def all_gather_columns(local: torch.Tensor, gathered: torch.Tensor | None = None
 
 
 def columns_view(gathered: torch.Tensor) -> torch.Tensor:
-    """(world, M, n_local) -> logical (M, world * n_local) as a strided view (no copy)."""
-    world, m, n_local = gathered.shape
-    return gathered.permute(1, 0, 2).reshape(m, world, n_local)
+    """(world, M, n_local) -> (M, world, n_local) strided view (no copy): ``view[i, r, j]`` is element
+    ``(i, r * n_local + j)`` of the logical (M, world * n_local) result.  The slabs are not adjacent in memory,
+    so the 2-D matrix itself needs a copy: ``columns_view(g).reshape(M, world * n_local)``."""
+    return gathered.permute(1, 0, 2)
 
 
 class ShardedFp4Linear:

@@ -136,7 +136,8 @@ int ave_fp4_pack_weight_tiles(const void* packed_row_major, int64_t n, int64_t k
  * D (m, n) bf16, row stride ldd elements  =  A (m, k) * B (n, k)^T, fp32 accumulation,
  * result scaled by (*a_global_scale) * (*b_global_scale) (NULL = 1) and rounded to
  * bf16 (nearest even).  Scales in AVE_FP4_SF_TILED layout.
- * Requirements: k % 32 == 0, ldd % 8 == 0, all pointers 16-byte aligned.
+ * Requirements: k % 32 == 0, n % 8 == 0, ldd % 8 == 0 (anything else is rejected with a negative return
+ * code before a launch: the write-out moves 8-column chunks), all pointers 16-byte aligned.
  * Stands in for the kernel launch of gemm_pipeline_transposed_b
  * (python/avelang_kernels/amdgpu_gemm.py:488-494).
  */

@@ -286,6 +286,17 @@ void ave_oracle_sf_to_tiled(const uint8_t *rowmajor, int64_t rows, int64_t ncol,
         }
 }
 
+/* Sets the OpenMP thread count of the loops above (launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1 to their workers; a CPU timing leg states its thread count explicitly instead). */
+void ave_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int ave_oracle_num_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -76,6 +76,8 @@ def lib() -> ctypes.CDLL:
         L.ave_oracle_f32_to_bf16.argtypes = [f32]
         L.ave_oracle_num_threads.restype = i32
         L.ave_oracle_num_threads.argtypes = []
+        L.ave_oracle_set_num_threads.restype = None
+        L.ave_oracle_set_num_threads.argtypes = [i32]
         L.ave_oracle_bias_act.restype = None
         L.ave_oracle_bias_act.argtypes = [vp, i64, i64, vp, i32, vp, vp]
         _lib = L
@@ -189,6 +191,11 @@ def c_sf_to_tiled(scales: np.ndarray) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().ave_oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads used by the C oracle's loops from now on (a timing leg states its thread count)."""
+    lib().ave_oracle_set_num_threads(int(n))
 
 
 # ----------------------------------------------------------------------- numpy

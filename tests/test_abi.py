@@ -119,3 +119,19 @@ def test_make_operand_accepts_torch_fp4_fp8_views():
     sc_mx = torch.full((4, 2), 127, dtype=torch.uint8)
     op = ave.make_operand(packed.view(torch.float4_e2m1fn_x2), sc_mx.view(torch.float8_e8m0fnu), None, ave.MXFP4)
     assert op.scales.dtype == torch.uint8 and op.k == 64
+
+
+def test_gemm_rejects_n_not_multiple_of_8_before_any_launch(lib):
+    """The write-out moves 8-column (16-byte) chunks, so a C-ABI caller with N % 8 != 0 must get a negative
+    return code instead of up to 7 columns written past N (the Python operators reject it earlier still)."""
+    dummy = ctypes.c_void_p(4096)   # never dereferenced: the argument check comes first
+    for entry in ("ave_fp4_gemm", "ave_fp4_gemm_epilogue"):
+        args = [dummy, dummy, None, dummy, dummy, None, dummy, 128, 132, 256, 136, 1, 0, None, 0, None]
+        if entry == "ave_fp4_gemm_epilogue":
+            args.append(None)
+        rc = getattr(lib, entry)(*args)
+        assert rc == -1, rc
+        assert b"N must be a multiple of 8" in lib.ave_fp4_last_error()
+    peers = (ctypes.c_void_p * 1)(4096)
+    rc = lib.ave_fp4_gemm_allgather(dummy, dummy, None, dummy, dummy, None, dummy, peers, 1, 128, 132, 256, 136, 1, 0, None)
+    assert rc == -1 and b"N must be a multiple of 8" in lib.ave_fp4_last_error()

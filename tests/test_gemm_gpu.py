@@ -84,6 +84,27 @@ def test_skinny_matches_oracle(cuda_device, oracle, fmt, m, n, k):
     _run_case(oracle, cuda_device, fmt, m, n, k, ave.GEMM_AUTO, a_kind="outlier")
 
 
+@pytest.mark.parametrize("fmt", [ave.NVFP4, ave.MXFP4])
+@pytest.mark.parametrize("m,n,k", [(16, 20480, 2048), (16, 19200, 1024), (8, 19072, 512), (32, 19072, 256)])
+def test_skinny_many_tiles_short_k(cuda_device, oracle, fmt, m, n, k):
+    """More weight tiles than SMs and a short K: the stream-K phase has fewer (tile, K block) units than there are
+    CTAs, so only some CTAs take part in it.  Every column must be written, and a second call must find the arrival
+    counters back at zero (same bits again)."""
+    a = inputs.make_operand_bf16("outlier", m, k, 5)
+    b = inputs.make_operand_bf16("weight", n, k, 6)
+    qa, qb = oracle.c_quantize(_bits(a), fmt), oracle.c_quantize(_bits(b), fmt)
+    _, dbf = oracle.c_gemm_fp4(qa, qb, fmt, want_f32=False)
+    A, B = _to_dev(qa, fmt, cuda_device), _to_dev(qb, fmt, cuda_device)
+    outs = []
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        _gemm(A, B, fmt, out=out, variant=ave.GEMM_SKINNY)
+        ave.check_device_status(cuda_device)
+        _check(out, dbf, oracle, f"fmt={fmt} {m}x{n}x{k} skinny, many tiles")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_skinny_is_deterministic_and_reusable(cuda_device, oracle):
     """Stream-K partials are added in a fixed order, and the scratch counters return to zero,
     so back-to-back calls give identical bits."""
