@@ -378,13 +378,42 @@ int skinny_burst(int stages) {
 
 int skinny_mp(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
 
+// Scratch of the decode kernel: [header 256 B][arrival counters][stream-K partials].  Everything that has to be zero
+// between launches (the header words and the counters) sits in a prefix whose size does not depend on the shape
+// (up to 4096 weight tiles, N = 524288), so one zero-initialised buffer can serve calls of different shapes one
+// after the other: what a call leaves behind in the partials never lands where another shape keeps a counter.
+constexpr int64_t kSkinnyHdrBytes = 256;
+constexpr int64_t kSkinnyCounterRegion = 64 * 1024;
+
 int64_t skinny_counter_bytes(int64_t n) {
     const int64_t tiles_n = (n + 127) / 128;
     return ((tiles_n * 4 * 4 + 255) / 256) * 256;
 }
 
+int64_t skinny_counter_region(int64_t n) {
+    const int64_t used = skinny_counter_bytes(n);
+    return used > kSkinnyCounterRegion ? used : kSkinnyCounterRegion;
+}
+
 int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
-    return skinny_counter_bytes(n) + static_cast<int64_t>(sm_count) * 2 * skinny_mp(m) * 128 * 4;
+    return kSkinnyHdrBytes + skinny_counter_region(n) + static_cast<int64_t>(sm_count) * 2 * skinny_mp(m) * 128 * 4;
+}
+
+// Scratch of ave_fp4_linear_decode: the decode kernel's scratch, then the quantised activations (MP rows of packed
+// bytes and their tiled scales; written for inspection by the kernel that quantises in shared memory, and the real
+// operand of the two-launch fallback), then two floats (tensor scale, amax) for that fallback.
+struct FusedScratch {
+    int64_t packed, sf, gs, total;
+};
+
+FusedScratch fused_scratch_layout(int64_t m, int64_t n, int64_t k, int vec, int sm_count) {
+    auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    FusedScratch f;
+    f.packed = up(skinny_workspace_bytes(m, n, sm_count));
+    f.sf = f.packed + up(static_cast<int64_t>(skinny_mp(m)) * (k / 2));
+    f.gs = f.sf + up(((k / vec + 3) / 4) * 512);
+    f.total = f.gs + 256;
+    return f;
 }
 
 template <int MP, int VEC, int ST>
@@ -420,8 +449,9 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.x_gs = xgs;
     p.w_gs = wgs;
     p.d = static_cast<__nv_bfloat16*>(d);
-    p.counters = static_cast<int*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + skinny_counter_bytes(n));
+    char* ws = static_cast<char*>(workspace);
+    p.counters = reinterpret_cast<int*>(ws + kSkinnyHdrBytes);
+    p.partials = reinterpret_cast<float*>(ws + kSkinnyHdrBytes + skinny_counter_region(n));
     p.status = ds.status;
     p.trace = ds.trace;
     p.trace_cap = ds.trace_cap;
@@ -493,8 +523,9 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
 constexpr int kNoAllocMaxM = 16;          // one MMA-N step of activation rows
 constexpr int kNoAllocMaxN = 65536;       // 512 weight tiles
 constexpr int kNoAllocMaxCtas = 160;      // persistent CTAs (one per SM)
-constexpr size_t kNoAllocCounterBytes = (kNoAllocMaxN / 128) * 4 * sizeof(int);                   // 8 KiB
+constexpr size_t kNoAllocCounterBytes = kSkinnyHdrBytes + kSkinnyCounterRegion;                    // header + counters, 64.25 KiB
 constexpr size_t kNoAllocPartialBytes = static_cast<size_t>(kNoAllocMaxCtas) * 2 * 16 * 128 * 4;  // 2.5 MiB
+static_assert((kNoAllocMaxN / 128) * 4 * sizeof(int) <= static_cast<size_t>(kSkinnyCounterRegion), "counters of the largest N must fit");
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocCounterBytes + kNoAllocPartialBytes];
 
 // Device address of the array per device.  The array's name is only a host-side handle for the
@@ -547,7 +578,7 @@ extern "C" int ave_fp4_gemm_decode_noalloc(const void* a_packed, const void* a_s
     if ((rc = noalloc_scratch_for_current_device(&scratch))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left: the arrival counters must start at zero.
-    AVE_CUDA(cudaMemsetAsync(scratch, 0, skinny_counter_bytes(n), s));
+    AVE_CUDA(cudaMemsetAsync(scratch, 0, kSkinnyHdrBytes + skinny_counter_bytes(n), s));
     const float* ags = static_cast<const float*>(a_global_scale);
     const float* bgs = static_cast<const float*>(b_global_scale);
     if (fmt == AVE_FP4_FMT_NVFP4)
@@ -734,6 +765,8 @@ int ave_fp4_quantize_nvfp4_dynamic(const void* x_bf16, int64_t rows, int64_t k, 
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(kFusedClusterCtas, 1, 1);
         cfg.blockDim = dim3(kFusedThreads, 1, 1);
+        const bool decode_sized = rows * (k / 16) <= kDecodeQuantBlocks;   // one 16-element block per thread
+        if (decode_sized) cfg.blockDim = dim3(kDecodeQuantThreads, 1, 1);
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits for its predecessor itself
@@ -744,6 +777,14 @@ int ave_fp4_quantize_nvfp4_dynamic(const void* x_bf16, int64_t rows, int64_t k, 
         float* gs = static_cast<float*>(global_scale);
         uint8_t* pk = static_cast<uint8_t*>(packed);
         uint8_t* sf = static_cast<uint8_t*>(scales);
+        if (decode_sized) {
+            int rows_i = static_cast<int>(rows), k_i = static_cast<int>(k);
+            if (sf_layout == AVE_FP4_SF_TILED)
+                AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_nvfp4_decode_kernel<true>, x, rows_i, k_i, ldx_ll, gs, pk, sf));
+            else
+                AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_nvfp4_decode_kernel<false>, x, rows_i, k_i, ldx_ll, gs, pk, sf));
+            return 0;
+        }
         if (sf_layout == AVE_FP4_SF_TILED)
             AVE_CUDA(cudaLaunchKernelEx(&cfg, quantize_nvfp4_fused_small_kernel<true>, x, rows_ll, k_ll, ldx_ll, gs, pk, sf));
         else
@@ -872,6 +913,64 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
             return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm: unknown variant %d", variant);
     }
 #undef GEMM_ARGS
+}
+
+int64_t ave_fp4_linear_decode_workspace_bytes(int64_t m, int64_t n, int64_t k, int fmt, int device) {
+    if (device < 0 || device >= kMaxDevices || !g_dev[device].ready) return -AVE_FP4_ERR_NOT_INIT;
+    if (m < 0 || n < 0 || k < 0 || m > 32) return -AVE_FP4_ERR_ARG;
+    return fused_scratch_layout(m, n, k, fmt == AVE_FP4_FMT_NVFP4 ? 16 : 32, g_dev[device].sm_count).total;
+}
+
+int ave_fp4_linear_decode(const void* x_bf16, int64_t ldx, const void* b_packed, const void* b_scales,
+                          const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt,
+                          int flags, void* workspace, int64_t workspace_bytes, void* stream, const ave_fp4_epilogue* epilogue) {
+    if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
+    if (m < 0 || n < 0 || k < 0 || n > 0x7fffffff || k > 0x7fffffff) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: size out of range");
+    if (m > 32)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode serves M <= 32 (got %lld); quantise with ave_fp4_quantize and call ave_fp4_gemm for more rows",
+                    static_cast<long long>(m));
+    if (flags & ~(AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS | AVE_FP4_LINEAR_FLAG_TILE_MAJOR_WEIGHTS))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: unknown flag bits 0x%x", flags);
+    DeviceState* ds = nullptr;
+    int rc = current_state(&ds);
+    if (rc) return rc;
+    if (m == 0 || n == 0) return 0;
+    if (k == 0 || k % 32 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: K must be a positive multiple of 32, got %lld", static_cast<long long>(k));
+    if (n % 8 != 0 || ldd < n || ldd % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: N and ldd must be multiples of 8 and ldd >= N");
+    if (ldx < k || ldx % 8 != 0) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: ldx must be >= K and a multiple of 8, got %lld", static_cast<long long>(ldx));
+    if (!x_bf16 || !b_packed || !b_scales || !d_bf16 || !aligned16(x_bf16) || !aligned16(b_packed) || !aligned16(b_scales) || !aligned16(d_bf16))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: null or misaligned (16-byte) pointer");
+    if (epilogue) {
+        if (epilogue->activation < AVE_FP4_ACT_NONE || epilogue->activation > AVE_FP4_ACT_SILU || epilogue->reserved != 0 || epilogue->quantize_out)
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: the epilogue takes a bias and an activation only");
+        if (epilogue->bias_bf16 && !aligned16(epilogue->bias_bf16)) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_linear_decode: bias must be 16-byte aligned");
+    }
+    const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
+    const int64_t need = fused_scratch_layout(m, n, k, nv ? 16 : 32, ds->sm_count).total;
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return fail(-AVE_FP4_ERR_WORKSPACE, "ave_fp4_linear_decode: workspace of %lld bytes (256-byte aligned, zero-initialised) required, got %lld",
+                    static_cast<long long>(need), static_cast<long long>(workspace ? workspace_bytes : 0));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float* bgs = static_cast<const float*>(b_global_scale);
+    const bool tile_major = (flags & AVE_FP4_LINEAR_FLAG_TILE_MAJOR_WEIGHTS) != 0;
+    const bool pdl = (flags & AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS) != 0;
+    const int mp = skinny_mp(m);
+    // quantise into the scratch (one launch: amax and quantise together for NVFP4), then the decode GEMM, chained by
+    // programmatic dependent launch: the GEMM's CTAs start and stream weights while the quantise still runs
+    const FusedScratch fq = fused_scratch_layout(m, n, k, nv ? 16 : 32, ds->sm_count);
+    char* ws = static_cast<char*>(workspace);
+    void* xq = ws + fq.packed;
+    void* xsf = ws + fq.sf;
+    float* xgs = nv ? reinterpret_cast<float*>(ws + fq.gs) : nullptr;
+    if (nv) {
+        if ((rc = ave_fp4_quantize_nvfp4_dynamic(x_bf16, m, k, ldx, xgs, xq, xsf, AVE_FP4_SF_TILED, xgs + 1, stream))) return rc;
+    } else {
+        if ((rc = ave_fp4_quantize(x_bf16, m, k, ldx, fmt, nullptr, nullptr, xq, xsf, AVE_FP4_SF_TILED, stream))) return rc;
+    }
+#define CHAIN_ARGS *ds, xq, xsf, xgs, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, workspace, tile_major, s, pdl, epilogue
+    if (mp == 16) return nv ? launch_skinny<16, 16, kStSkinny16>(CHAIN_ARGS) : launch_skinny<16, 32, kStSkinny16>(CHAIN_ARGS);
+    return nv ? launch_skinny<32, 16, kStSkinny32>(CHAIN_ARGS) : launch_skinny<32, 32, kStSkinny32>(CHAIN_ARGS);
+#undef CHAIN_ARGS
 }
 
 int ave_fp4_set_trace(void* buffer, int64_t bytes) {

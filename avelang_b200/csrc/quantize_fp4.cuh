@@ -215,6 +215,75 @@ __device__ __forceinline__ uint32_t quantize_block(const uint32_t* __restrict__ 
     return code;
 }
 
+// ---- NVFP4 items without branches on the common path --------------------------------------------------------
+// quantize_block picks one of three paths per block, and every such branch ends the stretch of code the compiler
+// can schedule as one, so a lane works through its blocks one dependent chain after the other.  The functions below
+// split the work in two phases over NI items (2 * NI blocks of 16 elements) held by one lane: first the scale
+// chain of every block (block maximum -> a / 6 / gs -> E4M3 code -> d = code value * gs -> -1 / d), all independent
+// of one another, then the element divisions of every block.  The common case needs no branch at all: a block whose
+// scale rounds to zero takes -0 as its "reciprocal" (every quotient becomes a zero of the sign opposite to x's,
+// which the final XOR turns into x's sign, exactly what the all-zero path of quantize_block writes), and the rare
+// cases the reciprocal method does not cover (a tiny non-zero maximum, a divisor with an all-ones significand or an
+// extreme exponent, a tensor scale that is not a plain divisor) raise a flag, upon which the lane redoes all of
+// its items with quantize_block.  The bytes are those of quantize_block in every case.
+__device__ __forceinline__ void nvfp4_scale_chain(const uint32_t* __restrict__ rw, float gs, float gs_recip, float sixth,
+                                                  uint32_t& code, float& d, float& nr, bool& rare) {
+    const uint32_t abits = block_amax_bits<8>(rw) << 16;
+    const float a = __uint_as_float(abits);
+    const float t = div_by_recip(a, 6.0f, sixth);
+    const float u = fminf(div_by_recip(t, gs, gs_recip), 448.0f);
+    code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
+    d = __fmul_rn(e4m3_decode(code), gs);
+    // a non-zero maximum below 2^-95 (its quotient by 6 may be subnormal) and divisors outside the theorem
+    rare = (abits - 1u < (32u << 23) - 1u) || (d != 0.0f && !divisor_is_plain(d));
+    nr = (d != 0.0f) ? -__frcp_rn(d) : -0.0f;
+}
+
+__device__ __forceinline__ void nvfp4_pack_block(const uint32_t* __restrict__ rw, float d, float nr, uint32_t* __restrict__ out_words) {
+    const float2 d2 = make_float2(d, d), nr2 = make_float2(nr, nr);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        float2 y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x2 = make_float2(__uint_as_float(rw[w * 4 + i] << 16), __uint_as_float(rw[w * 4 + i] & 0xffff0000u));
+            const float2 q0 = __fmul2_rn(x2, nr2);
+            const float2 t = __ffma2_rn(q0, d2, x2);
+            y[i] = __ffma2_rn(t, nr2, q0);
+        }
+        out_words[w] = pack8_e2m1_pairs(y) ^ 0x88888888u;
+    }
+}
+
+// NI items of 32 elements (rw[i][0..15] = 16 words of bf16 pairs) -> o[i][0..3] packed nibbles, codes[i] = the two
+// scale bytes (block 0 in bits 7:0, block 1 in bits 15:8).
+template <int NI>
+__device__ __forceinline__ void quantize_items_nvfp4(const uint32_t (&rw)[NI][16], float gs, bool gs_plain, float gs_recip, float sixth,
+                                                     uint32_t (&o)[NI][4], uint32_t (&codes)[NI]) {
+    uint32_t code[2 * NI];
+    float d[2 * NI], nr[2 * NI];
+    bool rare = !gs_plain;
+#pragma unroll
+    for (int b = 0; b < 2 * NI; ++b) {
+        bool r;
+        nvfp4_scale_chain(&rw[b >> 1][(b & 1) * 8], gs, gs_recip, sixth, code[b], d[b], nr[b], r);
+        rare = rare || r;
+    }
+    if (!rare) {
+#pragma unroll
+        for (int b = 0; b < 2 * NI; ++b) nvfp4_pack_block(&rw[b >> 1][(b & 1) * 8], d[b], nr[b], &o[b >> 1][(b & 1) * 2]);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) codes[i] = code[2 * i] | (code[2 * i + 1] << 8);
+    } else {
+#pragma unroll 1
+        for (int i = 0; i < NI; ++i) {
+            const uint32_t c0 = quantize_block<kFmtNvfp4>(&rw[i][0], gs, gs_plain, gs_recip, sixth, &o[i][0]);
+            const uint32_t c1 = quantize_block<kFmtNvfp4>(&rw[i][8], gs, gs_plain, gs_recip, sixth, &o[i][2]);
+            codes[i] = c0 | (c1 << 8);
+        }
+    }
+}
+
 // The quantise loop shared by the kernels below: warp `warp_global` of `warps_total` takes the
 // 1024-element steps warp_global, warp_global + warps_total, ... of the (rows, k) matrix.  Inside a
 // step lane L owns the 32 consecutive elements 32L .. 32L+31: four 128-bit loads (64 contiguous bytes),
@@ -259,18 +328,20 @@ __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ 
             continue;
         }
         const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + e);
-        uint32_t rw[16];
+        uint32_t rw1[1][16];
+        uint32_t (&rw)[16] = rw1[0];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint4 v = __ldg(src + i);
             rw[4 * i] = v.x; rw[4 * i + 1] = v.y; rw[4 * i + 2] = v.z; rw[4 * i + 3] = v.w;
         }
-        uint32_t o[4];
+        uint32_t o1[1][4];
+        uint32_t (&o)[4] = o1[0];
         uint32_t codes;
         if (FMT == kFmtNvfp4) {
-            const uint32_t c0 = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
-            const uint32_t c1 = quantize_block<FMT>(rw + 8, gs, gs_plain, gs_recip, sixth, o + 2);
-            codes = c0 | (c1 << 8);
+            uint32_t c1[1];
+            quantize_items_nvfp4<1>(rw1, gs, gs_plain, gs_recip, sixth, o1, c1);
+            codes = c1[0];
         } else {
             codes = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
         }
@@ -381,6 +452,85 @@ quantize_nvfp4_fused_small_kernel(const __nv_bfloat16* __restrict__ x, long long
     quantize_rows<kFmtNvfp4, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total);
     // no CTA may exit while another can still read its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Decode-sized activations (up to 8192 blocks of 16 elements, e.g. 16 x 8192): the same single launch of one 8-CTA
+// cluster, arranged for the shortest dependent chain, because the decode GEMM queued behind it can do nothing but
+// prefetch weights until these bytes exist.  One 16-element block per thread (8 x 1024 threads): the thread loads
+// its 32 bytes once and keeps them in registers across the cluster-wide amax exchange, so the chain is
+// load -> block maximum -> warp / CTA / cluster maximum -> one block's scale chain and 16 divisions -> store,
+// instead of two passes over memory with a 32-element item per lane.  Same bytes as the kernels above.
+constexpr int kDecodeQuantThreads = 1024;
+constexpr long long kDecodeQuantBlocks = static_cast<long long>(kFusedClusterCtas) * kDecodeQuantThreads;   // 8192
+
+template <bool TILED>
+__global__ void __cluster_dims__(kFusedClusterCtas, 1, 1) __launch_bounds__(kDecodeQuantThreads, 1)
+quantize_nvfp4_decode_kernel(const __nv_bfloat16* __restrict__ x, int rows, int k, long long ldx,
+                             float* __restrict__ gs_out, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+    __shared__ uint32_t s_warp[kDecodeQuantThreads / 32];
+    __shared__ uint32_t s_all[kFusedClusterCtas];     // every CTA's maximum, written here by the CTAs themselves
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int tid = threadIdx.x;
+    const int gtid = static_cast<int>(rank) * kDecodeQuantThreads + tid;
+    const int sf_cols = k / 16;
+    const int k_atoms = (sf_cols + 3) / 4;
+    const int blocks = rows * sf_cols;
+    const bool mine = gtid < blocks;
+    const int row = mine ? gtid / sf_cols : 0;
+    const int cb = mine ? gtid - row * sf_cols : 0;
+    uint32_t rw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    if (mine) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx + cb * 16);
+        const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+        rw[0] = v0.x; rw[1] = v0.y; rw[2] = v0.z; rw[3] = v0.w;
+        rw[4] = v1.x; rw[5] = v1.y; rw[6] = v1.z; rw[7] = v1.w;
+    }
+    if (TILED) {
+        // padding of the tiled scale layout (rows up to 128, scale columns up to a multiple of 4), independent of the data
+        const int rows_pad = ((rows + 127) / 128) * 128;
+        for (int i = gtid; i < rows_pad * k_atoms; i += static_cast<int>(kDecodeQuantBlocks)) {
+            const int r = i / k_atoms, a = i - r * k_atoms;
+            uint8_t* p = sf + sf_tiled_offset(r, a * 4, k_atoms);
+            if (r >= rows) {
+                *reinterpret_cast<uint32_t*>(p) = 0u;
+            } else {
+                for (int c = a * 4; c < a * 4 + 4; ++c)
+                    if (c >= sf_cols) p[c & 3] = 0;
+            }
+        }
+    }
+    // block maximum as bf16 bits (kept for the scale chain), then warp -> CTA -> cluster
+    const uint32_t a_bits = block_amax_bits<8>(rw);
+    uint32_t a = __reduce_max_sync(0xffffffffu, a_bits);
+    if ((tid & 31) == 0) s_warp[tid >> 5] = a;
+    __syncthreads();
+    if (tid < 32) {
+        a = __reduce_max_sync(0xffffffffu, s_warp[tid]);
+        // lane c pushes this CTA's maximum into slot `rank` of CTA c: after the one cluster barrier below every
+        // CTA finds all eight maxima in its own shared memory, and nobody reads a remote CTA afterwards
+        if (tid < kFusedClusterCtas) {
+            const uint32_t slot = static_cast<uint32_t>(__cvta_generic_to_shared(&s_all[rank]));
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(slot), "r"(tid));
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(a) : "memory");
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    uint32_t amax_bits = 0;
+#pragma unroll
+    for (int c = 0; c < kFusedClusterCtas; ++c) amax_bits = max(amax_bits, s_all[c]);
+    const float amax = __uint_as_float(amax_bits << 16);
+    const float gs = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 2688.0f);
+    if (gtid == 0) *gs_out = gs;
+    if (mine) {
+        uint32_t o[2];
+        const uint32_t code = quantize_block<kFmtNvfp4>(rw, gs, divisor_is_plain(gs), __frcp_rn(gs), __frcp_rn(6.0f), o);
+        *reinterpret_cast<uint2*>(packed + static_cast<long long>(row) * (k / 2) + cb * 8) = make_uint2(o[0], o[1]);
+        sf[TILED ? sf_tiled_offset(row, cb, k_atoms) : static_cast<long long>(row) * sf_cols + cb] = static_cast<uint8_t>(code);
+    }
 }
 
 // Row-major (rows, cols) scale bytes -> 128x4 tiled layout (padding zero).

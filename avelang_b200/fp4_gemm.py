@@ -370,6 +370,95 @@ def gemm_mxfp4_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | No
     return _gemm(A, B, out, MXFP4, variant, static_weights=static_weights, bias=bias, activation=activation)
 
 
+GEMM_FLAG_TILE_MAJOR_WEIGHTS = 0x200
+_decode_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _linear_decode(x: torch.Tensor, W: Fp4Operand, out: torch.Tensor | None, fmt: int, static_weights: bool,
+                   bias: torch.Tensor | None, activation: str | None) -> torch.Tensor:
+    name = _FMT_NAME[fmt]
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(k for k in ACTIVATIONS if k)}, got {activation!r}.")
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"x must have dtype torch.bfloat16, got {x.dtype}.")
+    if x.dim() != 2:
+        raise ValueError(f"x must be 2-D (M, K), got shape {tuple(x.shape)}.")
+    if W.fmt != fmt:
+        raise ValueError(f"W must be an {name} operand, got {_FMT_NAME.get(W.fmt, W.fmt)}.")
+    m, k = x.shape
+    n = W.rows
+    if W.k != k:
+        raise ValueError(f"x and W must share K, got {k} and {W.k}.")
+    if k % 32 != 0 or k == 0:
+        raise ValueError(f"K must be a positive multiple of 32, got {k}.")
+    if n % 8 != 0:
+        raise ValueError(f"N must be a multiple of 8, got {n}.")
+    dev = _require_cuda(x, "x")
+    if W.device != x.device:
+        raise ValueError(f"W must be on device {x.device}, got {W.device}.")
+    if x.stride(1) != 1 or (m > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        raise ValueError("x must be K-contiguous with a 16-byte aligned row stride.")
+    if fmt == NVFP4 and W.global_scale is None:
+        raise ValueError("an NVFP4 weight operand needs a global_scale tensor.")
+    if m > 32:
+        # more rows than the one-call decode entry point serves: the two operators, same results
+        q = _quantize(x, fmt, None, SF_TILED)
+        return _gemm(q, W, out, fmt, GEMM_AUTO, static_weights=static_weights, bias=bias, activation=activation)
+    out_shape = (m, n)
+    if out is None:
+        out = torch.empty(out_shape, dtype=torch.bfloat16, device=x.device)
+    elif tuple(out.shape) != out_shape:
+        raise ValueError(f"out must have shape {out_shape}, got {tuple(out.shape)}.")
+    elif out.dtype != torch.bfloat16:
+        raise ValueError(f"out must have dtype torch.bfloat16, got {out.dtype}.")
+    elif out.device != x.device:
+        raise ValueError(f"out must be on device {x.device}, got {out.device}.")
+    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
+    if bias is not None and (bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,) or bias.device != x.device
+                             or not bias.is_contiguous() or bias.data_ptr() % 16 != 0):
+        raise ValueError(f"bias must be a contiguous, 16-byte aligned bfloat16 tensor of shape ({n},) on {x.device}.")
+    if m == 0 or n == 0:
+        return out
+    W = to_tiled(W)
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        need = L.ave_fp4_linear_decode_workspace_bytes(m, n, k, fmt, dev)
+        if need < 0:
+            raise RuntimeError(f"ave-lang Error [CUDA]: workspace query failed ({need}).")
+        ws = _decode_workspaces.get(dev)
+        if ws is None or ws.numel() < need:
+            # zero-initialised once; the kernel leaves its counters at zero for the next call
+            ws = torch.zeros((need,), dtype=torch.uint8, device=x.device)
+            _decode_workspaces[dev] = ws
+        flags = (GEMM_FLAG_STATIC_WEIGHTS if static_weights else 0) | (GEMM_FLAG_TILE_MAJOR_WEIGHTS if W.tile_major else 0)
+        epi = None
+        if bias is not None or ACTIVATIONS[activation] != 0:
+            epi = ctypes.byref(_lib.Epilogue(None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], 0))
+        _lib.check(L.ave_fp4_linear_decode(_ptr(x), x.stride(0) if m > 1 else k, _ptr(W.packed), _ptr(W.scales), _ptr(W.global_scale),
+                                           _ptr(out), m, n, k, out.stride(0), fmt, flags, _ptr(ws), ws.numel(), _stream(x.device), epi))
+    return out
+
+
+def linear_nvfp4_decode(x: torch.Tensor, W: Fp4Operand, out: torch.Tensor | None = None, static_weights: bool = False,
+                        bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
+    """``act(quantize_nvfp4(x) @ W.T + bias)`` for bf16 activations x (M, K) and an NVFP4 weight operand W (N, K).
+
+    Up to M = 32 this is one call into the library that allocates nothing: the activations are quantised (tensor scale
+    from the data) into a scratch buffer and the decode GEMM is chained behind the quantise kernel with programmatic
+    dependent launch; results are bit-identical to ``gemm_nvfp4_transposed_b(quantize_nvfp4(x), W)``.  More rows take
+    that route through the two operators.  One scratch buffer per device is shared by every call on that device: keep
+    such calls on one stream.
+    """
+    return _linear_decode(x, W, out, NVFP4, static_weights, bias, activation)
+
+
+def linear_mxfp4_decode(x: torch.Tensor, W: Fp4Operand, out: torch.Tensor | None = None, static_weights: bool = False,
+                        bias: torch.Tensor | None = None, activation: str | None = None) -> torch.Tensor:
+    """``act(quantize_mxfp4(x) @ W.T + bias)``; see linear_nvfp4_decode."""
+    return _linear_decode(x, W, out, MXFP4, static_weights, bias, activation)
+
+
 def gemm_quantized_out_transposed_b(A: Fp4Operand, B: Fp4Operand, out_global_scale: torch.Tensor | None = None,
                                     bias: torch.Tensor | None = None, activation: str | None = None,
                                     sf_layout: int = SF_TILED, out_bf16: torch.Tensor | bool | None = None,

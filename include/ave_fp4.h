@@ -182,6 +182,32 @@ int ave_fp4_gemm_epilogue(const void* a_packed, const void* a_scales, const void
                           const ave_fp4_epilogue* epilogue);
 
 /*
+ * Decode-shaped linear layer on unquantised activations (M <= 32), in one call that allocates nothing:
+ *   D (m, n) bf16 = act(quantise(X) * B^T + bias),  X (m, k) bf16 with row stride ldx elements.
+ * X is quantised to the GEMM's format into the caller's scratch exactly as ave_fp4_quantize /
+ * ave_fp4_quantize_nvfp4_dynamic would (NVFP4: tensor scale amax / 2688 taken from X; up to 8192 blocks of 16
+ * elements, e.g. 16 x 8192, by one 8-CTA cluster launch with one block per thread, amax and quantise together), and the
+ * decode GEMM is chained behind it with programmatic dependent launch, so its CTAs start and stream weights while
+ * the quantise still runs.  D is bit-identical to ave_fp4_quantize* followed by ave_fp4_gemm (decode variant).
+ * (Quantising inside the GEMM kernel itself was built and measured and is not shipped: every CTA needs all of X,
+ * and the exact-division quantise costs about ten instructions per element, so doing it redundantly per CTA, or
+ * exchanging the bytes between CTAs through memory with its ~3 us loaded latency, was slower than this chain.)
+ * `workspace`: ave_fp4_linear_decode_workspace_bytes(...) bytes, 256-byte aligned, all zero before its first use;
+ * the call leaves it reusable for the next call on the same stream (calls that may overlap on the GPU need
+ * separate workspaces).  After the call it holds the quantised activations (layout private).
+ * `flags`: AVE_FP4_GEMM_FLAG_STATIC_WEIGHTS (as for ave_fp4_gemm) and/or AVE_FP4_LINEAR_FLAG_TILE_MAJOR_WEIGHTS
+ * (b_packed in the layout of ave_fp4_pack_weight_tiles).  `epilogue`: NULL, or bias and activation (no quantize_out).
+ * Stands in for the prologue + launch of gemm_pipeline_transposed_b (python/avelang_kernels/amdgpu_gemm.py:392-401,
+ * 488-494) when the activations arrive unquantised; the reference has no quantise step of its own.
+ */
+#define AVE_FP4_LINEAR_FLAG_TILE_MAJOR_WEIGHTS 0x200
+int64_t ave_fp4_linear_decode_workspace_bytes(int64_t m, int64_t n, int64_t k, int fmt, int device);
+int ave_fp4_linear_decode(const void* x_bf16, int64_t ldx, const void* b_packed, const void* b_scales,
+                          const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt,
+                          int flags, void* workspace, int64_t workspace_bytes, void* stream,
+                          const ave_fp4_epilogue* epilogue);
+
+/*
  * The reference operator itself on sm_100a: D (m, n) bf16 = A (m, k) bf16 * B (n, k)^T bf16, fp32 accumulation in
  * tensor memory (tcgen05.mma kind::f16), bf16 output rounded to nearest even (the reference's MI300 kernel
  * truncates, python/avelang_kernels/amdgpu_gemm.py:322-328).  K % 8 == 0, ldd % 8 == 0, 16-byte aligned pointers;
