@@ -284,6 +284,84 @@ __device__ __forceinline__ void quantize_items_nvfp4(const uint32_t (&rw)[NI][16
     }
 }
 
+// ---- per-launch tables for the scale chain ------------------------------------------------------------------
+// With the tensor scale fixed for a launch, the scale chain of a block depends only on the block maximum a, a bf16
+// value m * 2^e with one of 128 significands m in [1, 2):  RN(RN(a / 6) / gs) = RN(RN(m / 6) / gs) * 2^e, because
+// scaling by a power of two is exact as long as nothing leaves the normal range (outside it the E4M3 code is 0 or
+// saturates either way).  So a CTA computes u_m = RN(RN(m / 6) / gs) once for the 128 significands with true
+// divisions, and for each of the 127 E4M3 codes the divisor d = value(code) * gs with its negated reciprocal; a
+// block then needs two shared-memory reads, a multiply by 2^e and the E4M3 conversion instead of two emulated
+// divisions, a decode, a reciprocal and the checks on d.  An entry whose divisor the reciprocal method does not
+// cover carries +0 as its reciprocal (a real one is negative, a zero divisor has -0), which sends the lane to
+// quantize_block like the other rare cases.  `usable` is false when gs is so large or small that u_m itself
+// leaves the normal range; the launch then takes the path without tables.
+struct Nvfp4Tables {
+    float u[128];        // u_m for m = 1 + i / 128
+    float2 dn[128];      // (d, -1/d) per E4M3 code 0 .. 126 (127 unused)
+    int usable;
+};
+
+__device__ __forceinline__ void nvfp4_build_tables(Nvfp4Tables& t, float gs, int tid, int nthreads) {
+    if (tid == 0) t.usable = 1;
+    __syncthreads();
+    for (int i = tid; i < 256; i += nthreads) {
+        if (i < 128) {
+            const float m = __uint_as_float(0x3f800000u | (static_cast<uint32_t>(i) << 16));
+            const float u = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
+            t.u[i] = u;
+            const uint32_t e = (__float_as_uint(u) >> 23) & 0xffu;
+            if (e < 40u || e > 214u) t.usable = 0;     // scaling by 2^e of any bf16 maximum must stay exact (or saturate)
+        } else {
+            const uint32_t c = static_cast<uint32_t>(i - 128);
+            const float d = __fmul_rn(e4m3_decode(c), gs);
+            float nr = -0.0f;
+            if (d != 0.0f) nr = divisor_is_plain(d) ? -__frcp_rn(d) : 0.0f;
+            t.dn[c] = make_float2(d, nr);
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void nvfp4_scale_chain_tab(const uint32_t* __restrict__ rw, const Nvfp4Tables& t,
+                                                      uint32_t& code, float& d, float& nr, bool& rare) {
+    const uint32_t abits = block_amax_bits<8>(rw) << 16;
+    const float u = fminf(__fmul_rn(t.u[(abits >> 16) & 0x7fu], __uint_as_float(abits & 0x7f800000u)), 448.0f);
+    code = static_cast<uint32_t>(__nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3));
+    const float2 dn = t.dn[code];
+    d = dn.x;
+    nr = dn.y;
+    // a non-zero maximum below 2^-95 (its quotient by 6 may be subnormal) and divisors outside the theorem
+    rare = (abits - 1u < (32u << 23) - 1u) || (__float_as_uint(nr) == 0u);
+}
+
+// As quantize_items_nvfp4, with the scale chains read from the launch's tables.
+template <int NI>
+__device__ __forceinline__ void quantize_items_nvfp4_tab(const uint32_t (&rw)[NI][16], const Nvfp4Tables& t, float gs, bool gs_plain,
+                                                         float gs_recip, float sixth, uint32_t (&o)[NI][4], uint32_t (&codes)[NI]) {
+    uint32_t code[2 * NI];
+    float d[2 * NI], nr[2 * NI];
+    bool rare = false;
+#pragma unroll
+    for (int b = 0; b < 2 * NI; ++b) {
+        bool r;
+        nvfp4_scale_chain_tab(&rw[b >> 1][(b & 1) * 8], t, code[b], d[b], nr[b], r);
+        rare = rare || r;
+    }
+    if (!rare) {
+#pragma unroll
+        for (int b = 0; b < 2 * NI; ++b) nvfp4_pack_block(&rw[b >> 1][(b & 1) * 8], d[b], nr[b], &o[b >> 1][(b & 1) * 2]);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) codes[i] = code[2 * i] | (code[2 * i + 1] << 8);
+    } else {
+#pragma unroll 1
+        for (int i = 0; i < NI; ++i) {
+            const uint32_t c0 = quantize_block<kFmtNvfp4>(&rw[i][0], gs, gs_plain, gs_recip, sixth, &o[i][0]);
+            const uint32_t c1 = quantize_block<kFmtNvfp4>(&rw[i][8], gs, gs_plain, gs_recip, sixth, &o[i][2]);
+            codes[i] = c0 | (c1 << 8);
+        }
+    }
+}
+
 // The quantise loop shared by the kernels below: warp `warp_global` of `warps_total` takes the
 // 1024-element steps warp_global, warp_global + warps_total, ... of the (rows, k) matrix.  Inside a
 // step lane L owns the 32 consecutive elements 32L .. 32L+31: four 128-bit loads (64 contiguous bytes),
@@ -292,7 +370,7 @@ __device__ __forceinline__ void quantize_items_nvfp4(const uint32_t (&rw)[NI][16
 template <int FMT, bool TILED>
 __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ x, long long rows, long long k, long long ldx,
                                               float gs, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf,
-                                              long long warp_global, long long warps_total) {
+                                              long long warp_global, long long warps_total, const Nvfp4Tables* tab = nullptr) {
     constexpr int BLK = (FMT == kFmtNvfp4) ? 16 : 32;
     const int lane = threadIdx.x & 31;
     // a / 6 / gs is needed once per block; both divisors are fixed for the launch
@@ -313,11 +391,34 @@ __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ 
     int ch = static_cast<int>(warp_global - r * chunks);
     const long long step_r = warps_total / chunks;
     const int step_c = static_cast<int>(warps_total - step_r * chunks);
-    for (long long item = warp_global; item < items; item += warps_total, r += step_r, ch += step_c) {
-        if (ch >= chunks) { ch -= chunks; ++r; }
+    // The loads of the next item are issued before the arithmetic of the current one, so that a warp always has
+    // 64 bytes per lane on their way while it computes (the scale chain and the exact divisions are long enough
+    // for memory latency to show otherwise).
+    auto fetch = [&](long long rr, int cc, uint32_t (&dst)[16]) -> bool {
+        const int e = cc * 1024 + lane * 32;
+        const bool in = (rr < rows) && (e < kk);
+        if (in) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + rr * ldx + e);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = __ldg(src + i);
+                dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+            }
+        }
+        return in;
+    };
+    uint32_t rw1[1][16];
+    uint32_t (&rw)[16] = rw1[0];
+    bool in = (warp_global < items) && fetch(r, ch, rw);
+    for (long long item = warp_global; item < items; item += warps_total) {
+        // next item of this warp
+        long long rn = r + step_r;
+        int cn = ch + step_c;
+        if (cn >= chunks) { cn -= chunks; ++rn; }
+        uint32_t nx[16];
+        const bool in_next = (item + warps_total < items) && fetch(rn, cn, nx);
         const int e = ch * 1024 + lane * 32;   // this lane's first element
-        const int c = e / BLK;                                                  // ... and first scale column
-        const bool in = (r < rows) && (e < kk);
+        const int c = e / BLK;                 // ... and first scale column
         if (!in) {
             // padding of the tiled scale layout (rows up to a multiple of 128, columns of 4): zero bytes
             if (TILED && e < k_pad) {
@@ -325,30 +426,28 @@ __device__ __forceinline__ void quantize_rows(const __nv_bfloat16* __restrict__ 
                 if (FMT == kFmtNvfp4) *reinterpret_cast<uint16_t*>(p) = 0;
                 else *p = 0;
             }
-            continue;
-        }
-        const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + e);
-        uint32_t rw1[1][16];
-        uint32_t (&rw)[16] = rw1[0];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 v = __ldg(src + i);
-            rw[4 * i] = v.x; rw[4 * i + 1] = v.y; rw[4 * i + 2] = v.z; rw[4 * i + 3] = v.w;
-        }
-        uint32_t o1[1][4];
-        uint32_t (&o)[4] = o1[0];
-        uint32_t codes;
-        if (FMT == kFmtNvfp4) {
-            uint32_t c1[1];
-            quantize_items_nvfp4<1>(rw1, gs, gs_plain, gs_recip, sixth, o1, c1);
-            codes = c1[0];
         } else {
-            codes = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
+            uint32_t o1[1][4];
+            uint32_t (&o)[4] = o1[0];
+            uint32_t codes;
+            if (FMT == kFmtNvfp4) {
+                uint32_t c1[1];
+                if (tab != nullptr) quantize_items_nvfp4_tab<1>(rw1, *tab, gs, gs_plain, gs_recip, sixth, o1, c1);
+                else quantize_items_nvfp4<1>(rw1, gs, gs_plain, gs_recip, sixth, o1, c1);
+                codes = c1[0];
+            } else {
+                codes = quantize_block<FMT>(rw, gs, gs_plain, gs_recip, sixth, o);
+            }
+            __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e / 2), make_uint4(o[0], o[1], o[2], o[3]));
+            uint8_t* p = TILED ? sf + sf_tiled_offset(r, c, k_atoms) : sf + r * sf_cols + c;
+            if (FMT == kFmtNvfp4) *reinterpret_cast<uint16_t*>(p) = static_cast<uint16_t>(codes);   // columns c, c+1 (c even)
+            else *p = static_cast<uint8_t>(codes);
         }
-        __stcs(reinterpret_cast<uint4*>(packed + r * (kk / 2) + e / 2), make_uint4(o[0], o[1], o[2], o[3]));
-        uint8_t* p = TILED ? sf + sf_tiled_offset(r, c, k_atoms) : sf + r * sf_cols + c;
-        if (FMT == kFmtNvfp4) *reinterpret_cast<uint16_t*>(p) = static_cast<uint16_t>(codes);   // columns c, c+1 (c even)
-        else *p = static_cast<uint8_t>(codes);
+        r = rn;
+        ch = cn;
+        in = in_next;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) rw[i] = nx[i];
     }
 }
 
@@ -374,7 +473,13 @@ quantize_fp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
             gs = *gs_io;
         }
     }
-    quantize_rows<FMT, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total);
+    if constexpr (FMT == kFmtNvfp4) {
+        __shared__ Nvfp4Tables tab;
+        nvfp4_build_tables(tab, gs, threadIdx.x, blockDim.x);
+        quantize_rows<FMT, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total, tab.usable ? &tab : nullptr);
+    } else {
+        quantize_rows<FMT, TILED>(x, rows, k, ldx, gs, packed, sf, warp_global, warps_total);
+    }
 }
 
 // Small activations (decode: 16 x 8192): tensor amax and NVFP4 quantise in ONE launch of one
