@@ -99,9 +99,24 @@ constexpr int kSt1N128 = 5, kSt1N256 = 3, kSt2N256 = 5, kSt2N128 = 6, kSt2N192 =
 constexpr int kStDense2N256 = 6, kStDense1N128 = 6;   // dense bf16: 32 KB per stage
 constexpr int kStSkinny16 = 8, kStSkinny32 = 8, kStSkinny64 = 7;
 
+// Pipeline-depth tuning aid: the NVFP4 256x256 CTA-pair tile with 3 and 4 stages (plain epilogue only), chosen with
+// AVE_FP4_GEMM_STAGES; the depth used otherwise is kSt2N256.
+int tuning_stages_2n256() {
+    static const int v = [] { const char* e = getenv("AVE_FP4_GEMM_STAGES"); return e ? atoi(e) : 0; }();
+    return v;
+}
+
+template <int ST>
+cudaError_t prepare_gemm_plain_2n256() {
+    return cudaFuncSetAttribute(gemm_fp4_kernel<2, 256, 16, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmConfig<2, 256, 16, ST, 1>::kSmemBytes);
+}
+
 cudaError_t prepare_all() {
     cudaError_t e;
 #define PREP(x) if ((e = (x)) != cudaSuccess) return e;
+    PREP((prepare_gemm_plain_2n256<3>()));
+    PREP((prepare_gemm_plain_2n256<4>()));
     PREP((prepare_gemm<1, 128, 16, kSt1N128, 2>()));
     PREP((prepare_gemm<1, 128, 32, kSt1N128, 2>()));
     PREP((prepare_gemm<1, 256, 16, kSt1N256, 1>()));
@@ -229,7 +244,7 @@ int tiled_pdl(const DeviceState& ds) {
 }
 
 // ----------------------------------------------------------------------------------
-template <int CG, int BN, int VEC, int ST, int ACC>
+template <int CG, int BN, int VEC, int ST, int ACC, bool PLAIN_ONLY = false>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
                 void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr,
@@ -301,7 +316,11 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 2 : 1;
-    if (rs_world > 0) {
+    if constexpr (PLAIN_ONLY) {
+        if (rs_world > 0 || quant || p.bias != nullptr || p.act != 0)
+            return fail(-AVE_FP4_ERR_ARG, "this tuning instantiation has the plain epilogue only");
+        AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC>, tm_a, tm_b, tm_sfa, tm_sfb, p));
+    } else if (rs_world > 0) {
         if constexpr (CG == 2 && BN == 256)
             AVE_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<CG, BN, VEC, ST, ACC, kEpiPartial>, tm_a, tm_b, tm_sfa, tm_sfb, p));
         else
@@ -446,6 +465,9 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.w_tile_major = w_tile_major ? 1 : 0;
     p.pdl = pdl ? 1 : 0;
     p.burst = skinny_burst(ST);
+    // AVE_FP4_SKINNY_STREAMK=0: whole tiles only (tuning aid: the schedule the two-phase stream-K split is measured against)
+    static const bool no_streamk = [] { const char* e = getenv("AVE_FP4_SKINNY_STREAMK"); return e != nullptr && e[0] == '0'; }();
+    p.no_streamk = no_streamk ? 1 : 0;
     p.x_gs = xgs;
     p.w_gs = wgs;
     p.d = static_cast<__nv_bfloat16*>(d);
@@ -458,7 +480,7 @@ int launch_skinny(const DeviceState& ds, const void* x, const void* sfx, const f
     p.bias = epi ? static_cast<const __nv_bfloat16*>(epi->bias_bf16) : nullptr;
     p.act = epi ? epi->activation : 0;
 
-    const long long units = static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
+    const long long units = no_streamk ? static_cast<long long>(p.tiles_n) : static_cast<long long>(p.tiles_n) * ((k + 255) / 256);
     long long grid = ds.sm_count;
     if (units < grid) grid = units;
     cudaLaunchConfig_t cfg;
@@ -888,6 +910,8 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
         case AVE_FP4_GEMM_1CTA_N256:
             return nv ? launch_gemm<1, 256, 16, kSt1N256, 1>(GEMM_ARGS) : launch_gemm<1, 256, 32, kSt1N256, 1>(GEMM_ARGS);
         case AVE_FP4_GEMM_2CTA_N256:
+            if (nv && epi == nullptr && rs_world == 0 && tuning_stages_2n256() == 3) return launch_gemm<2, 256, 16, 3, 1, true>(GEMM_ARGS);
+            if (nv && epi == nullptr && rs_world == 0 && tuning_stages_2n256() == 4) return launch_gemm<2, 256, 16, 4, 1, true>(GEMM_ARGS);
             return nv ? launch_gemm<2, 256, 16, kSt2N256, 1>(GEMM_ARGS) : launch_gemm<2, 256, 32, kSt2N256, 1>(GEMM_ARGS);
         case AVE_FP4_GEMM_2CTA_N128:
             return nv ? launch_gemm<2, 128, 16, kSt2N128, 2>(GEMM_ARGS) : launch_gemm<2, 128, 32, kSt2N128, 2>(GEMM_ARGS);

@@ -36,6 +36,7 @@ struct SkinnyParams {
                           //    previous kernel in the stream has finished, everything else waits for it
     int burst;            // K blocks whose loads are issued together (1 .. min(8, STAGES))
     int w_tile_major;     // 0: W packed row-major (N, K/2); 1: 16 KB tiles [N/128][K/256][128 rows][128 B]
+    int no_streamk;       // 1: whole tiles only, tile t on CTA t mod G (the schedule the stream-K split is measured against)
     const float* x_gs;    // device fp32 tensor scales or nullptr
     const float* w_gs;
     __nv_bfloat16* d;
@@ -97,8 +98,10 @@ gemm_fp4_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int lane = threadIdx.x & 31;
     const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
     const long long ctas = gridDim.x;
-    const int whole_tiles = p.tiles_n / static_cast<int>(gridDim.x);            // whole tiles per CTA (second phase)
-    const int sk_tiles = p.tiles_n - whole_tiles * static_cast<int>(gridDim.x);  // tiles 0 .. sk_tiles-1 are split stream-K
+    // whole tiles per CTA (second phase); tiles 0 .. sk_tiles-1 are split stream-K
+    const int whole_tiles = p.no_streamk ? (p.tiles_n - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                                         : p.tiles_n / static_cast<int>(gridDim.x);
+    const int sk_tiles = p.no_streamk ? 0 : p.tiles_n - whole_tiles * static_cast<int>(gridDim.x);
     const long long units = static_cast<long long>(sk_tiles) * num_kb;           // stream-K units, cut into equal ranges
     // Only min(G, units) CTAs take part in the stream-K phase, so that every one of them owns at least one unit:
     // the finish test below counts one contribution from every CTA between the first and the last owner of a tile.
