@@ -29,7 +29,7 @@ EXPORTS = (
     "ave_fp4_quantize", "ave_fp4_sf_to_tiled", "ave_fp4_gemm", "ave_fp4_check", "ave_fp4_sm_count", "ave_fp4_set_trace",
     "ave_fp4_weight_tiles_bytes", "ave_fp4_pack_weight_tiles", "ave_fp4_gemm_decode_noalloc", "ave_fp4_gemm_allgather", "ave_fp4_quantize_nvfp4_dynamic", "ave_bf16_gemm", "ave_fp4_selftest_wait_timeout",
     "ave_fp4_gemm_epilogue", "ave_fp4_gemm_partials", "ave_fp4_reduce_partials",
-    "ave_fp4_linear_decode", "ave_fp4_linear_decode_workspace_bytes",
+    "ave_fp4_linear_decode", "ave_fp4_linear_decode_workspace_bytes", "ave_fp4_gemm_allgather_quantized",
 )
 
 
@@ -90,6 +90,9 @@ def load() -> ctypes.CDLL:
         L.ave_fp4_linear_decode_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
         L.ave_fp4_linear_decode.restype = i32
         L.ave_fp4_linear_decode.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, i64, vp, ctypes.POINTER(Epilogue)]
+        L.ave_fp4_gemm_allgather_quantized.restype = i32
+        L.ave_fp4_gemm_allgather_quantized.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, ctypes.POINTER(Epilogue), i64, i64,
+                                                       ctypes.POINTER(vp), ctypes.POINTER(vp), i32, vp]
         L.ave_fp4_set_trace.restype = i32
         L.ave_fp4_set_trace.argtypes = [vp, i64]
         _lib = L

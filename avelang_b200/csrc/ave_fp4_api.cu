@@ -244,11 +244,21 @@ int tiled_pdl(const DeviceState& ds) {
 }
 
 // ----------------------------------------------------------------------------------
+// Where a quantised result goes when it is one column block of a wider operand that all ranks gather
+// (ave_fp4_gemm_allgather_quantized); null = the result is an operand of its own.
+struct QuantGather {
+    int64_t n_total;            // columns of the gathered operand
+    int64_t col0;               // first column of this rank's block in it
+    void* const* peer_packed;   // the operand's packed bytes / scales in the other ranks' memory (base addresses)
+    void* const* peer_sf;
+    int n_peers;
+};
+
 template <int CG, int BN, int VEC, int ST, int ACC, bool PLAIN_ONLY = false>
 int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const float* ags, const void* b, const void* sfb,
                 const float* bgs, void* d, int64_t m, int64_t n, int64_t k, int64_t ldd, cudaStream_t stream,
                 void* const* peers = nullptr, int n_peers = 0, const ave_fp4_epilogue* epi = nullptr,
-                void* const* slabs = nullptr, int rs_world = 0, int first_owner = 0) {
+                void* const* slabs = nullptr, int rs_world = 0, int first_owner = 0, const QuantGather* qg = nullptr) {
     using Cfg = GemmConfig<CG, BN, VEC, ST, ACC>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc;
@@ -280,6 +290,20 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
     p.q_sf = quant ? static_cast<uint8_t*>(epi->q_scales) : nullptr;
     p.q_gs = quant ? static_cast<const float*>(epi->q_global_scale) : nullptr;
     p.q_tiled = (quant && epi->q_sf_layout == AVE_FP4_SF_TILED) ? 1 : 0;
+    {
+        const int64_t blk = (VEC == 0) ? 16 : VEC;
+        const int64_t q_n = qg ? qg->n_total : n;
+        const int64_t q_c0 = qg ? qg->col0 : 0;
+        p.q_ld = static_cast<int>(q_n / 2);
+        p.q_sf_cols = static_cast<int>(q_n / blk);
+        p.q_sf_col0 = static_cast<int>(q_c0 / blk);
+        if (quant) p.q_packed += q_c0 / 2;      // this rank's column block; the scale offset is applied per scale column
+        p.q_n_peers = (quant && qg) ? qg->n_peers : 0;
+        for (int i = 0; i < 7; ++i) {
+            p.q_peer_packed[i] = (i < p.q_n_peers) ? static_cast<uint8_t*>(qg->peer_packed[i]) + q_c0 / 2 : nullptr;
+            p.q_peer_sf[i] = (i < p.q_n_peers) ? static_cast<uint8_t*>(qg->peer_sf[i]) : nullptr;
+        }
+    }
     p.pdl = tiled_pdl(ds);
     p.rs_world = rs_world;
     p.rs_rows = rs_world > 0 ? static_cast<int>(m / rs_world) : 0;
@@ -509,11 +533,15 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
     // Tiled kernels: estimate the time of each tile shape as (waves of tiles over the SMs) x (tile work) /
     // (how well that shape feeds the tensor pipe, measured at 8192^3), and take the smallest.  Large problems
     // get 256x256 CTA-pair tiles; problems with few tiles get smaller tiles so that more SMs have work.
+    // eff = TFLOP/s of the shape relative to the 256x256 CTA-pair tile, measured at 8192^3 with every tile shape
+    // (5783 / 5368 / 4951 / 4826 / 4394 TFLOP/s; tensor pipe active 85 / 79 / 72 / 69 / 61 %; the same order and
+    // ratios at 8192 x 7168 x 8192).
     struct Cand { int variant; int cta_m, bn, group; double eff; };
     static const Cand cands[] = {
         {AVE_FP4_GEMM_2CTA_N256, 256, 256, 2, 1.00},
-        {AVE_FP4_GEMM_2CTA_N128, 256, 128, 2, 0.87},
-        {AVE_FP4_GEMM_1CTA_N256, 128, 256, 1, 0.84},
+        {AVE_FP4_GEMM_2CTA_N192, 256, 192, 2, 0.93},
+        {AVE_FP4_GEMM_2CTA_N128, 256, 128, 2, 0.86},
+        {AVE_FP4_GEMM_1CTA_N256, 128, 256, 1, 0.83},
         {AVE_FP4_GEMM_1CTA_N128, 128, 128, 1, 0.76},
     };
     int sms = 148;
@@ -861,7 +889,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
                       const void* b_scales, const void* b_global_scale, void* d_bf16, int64_t m, int64_t n, int64_t k,
                       int64_t ldd, int fmt, int variant, void* workspace, int64_t workspace_bytes, void* stream,
                       void* const* peers, int n_peers, const ave_fp4_epilogue* epi = nullptr, void* const* slabs = nullptr,
-                      int rs_world = 0, int first_owner = 0) {
+                      int rs_world = 0, int first_owner = 0, const QuantGather* qg = nullptr) {
     // shape and pointer rules first (they need no device), then the per-device state
     if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
     if (m < 0 || n < 0 || k < 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
@@ -903,7 +931,7 @@ static int gemm_entry(const void* a_packed, const void* a_scales, const void* a_
         v = AVE_FP4_GEMM_1CTA_N128;   // the quantising epilogue lives in the tiled kernels
     const bool nv = (fmt == AVE_FP4_FMT_NVFP4);
 
-#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi, slabs, rs_world, first_owner
+#define GEMM_ARGS *ds, a_packed, a_scales, ags, b_packed, b_scales, bgs, d_bf16, m, n, k, ldd, s, peers, n_peers, epi, slabs, rs_world, first_owner, qg
     switch (v) {
         case AVE_FP4_GEMM_1CTA_N128:
             return nv ? launch_gemm<1, 128, 16, kSt1N128, 2>(GEMM_ARGS) : launch_gemm<1, 128, 32, kSt1N128, 2>(GEMM_ARGS);
@@ -1081,6 +1109,32 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
     if (variant == AVE_FP4_GEMM_AUTO) variant = AVE_FP4_GEMM_2CTA_N256;
     return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, d_bf16, m, n, k, ldd, fmt,
                       variant, nullptr, 0, stream, peer_d, n_peers);
+}
+
+int ave_fp4_gemm_allgather_quantized(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                                     const void* b_scales, const void* b_global_scale, int64_t m, int64_t n, int64_t k, int fmt,
+                                     int variant, const ave_fp4_epilogue* epilogue, int64_t n_total, int64_t col0,
+                                     void* const* peer_q_packed, void* const* peer_q_scales, int n_peers, void* stream) {
+    if (fmt != AVE_FP4_FMT_NVFP4 && fmt != AVE_FP4_FMT_MXFP4) return fail(-AVE_FP4_ERR_ARG, "unknown format %d", fmt);
+    if (epilogue == nullptr || !epilogue->quantize_out)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: the epilogue must ask for the quantised result (quantize_out)");
+    if (n_peers < 0 || n_peers > 7) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: 0..7 peers supported, got %d", n_peers);
+    if (n_peers > 0 && (peer_q_packed == nullptr || peer_q_scales == nullptr))
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: peer pointer arrays are NULL");
+    for (int i = 0; i < n_peers; ++i)
+        if (!peer_q_packed[i] || !peer_q_scales[i] || !aligned16(peer_q_packed[i]) || !aligned16(peer_q_scales[i]))
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: peer pointer %d is null or misaligned", i);
+    // every rank's block is whole 64-column groups (32 packed bytes, 4 NVFP4 / 2 MXFP4 scale columns of one tile row)
+    if (n <= 0 || n % 64 != 0 || col0 < 0 || col0 % 64 != 0 || n_total % 64 != 0 || col0 + n > n_total)
+        return fail(-AVE_FP4_ERR_ARG,
+                    "ave_fp4_gemm_allgather_quantized: N, col0 and n_total must be multiples of 64 with col0 + N <= n_total "
+                    "(got N = %lld, col0 = %lld, n_total = %lld)", static_cast<long long>(n), static_cast<long long>(col0),
+                    static_cast<long long>(n_total));
+    if (m <= 64) return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized is served by the tiled kernels only (M > 64)");
+    if (variant == AVE_FP4_GEMM_AUTO) variant = AVE_FP4_GEMM_2CTA_N256;
+    QuantGather qg{n_total, col0, peer_q_packed, peer_q_scales, n_peers};
+    return gemm_entry(a_packed, a_scales, a_global_scale, b_packed, b_scales, b_global_scale, nullptr, m, n, k, n, fmt, variant,
+                      nullptr, 0, stream, nullptr, 0, epilogue, nullptr, 0, 0, &qg);
 }
 
 int ave_bf16_gemm(const void* a_bf16, const void* b_bf16, void* d_bf16, int64_t m, int64_t n, int64_t k, int64_t ldd,

@@ -71,6 +71,13 @@ struct GemmParams {
     uint8_t* q_sf;             // scale bytes, layout q_tiled
     const float* q_gs;         // NVFP4: device fp32 tensor scale of the result (static)
     int q_tiled;               // 1: 128x4 tiled scale layout (padding written as zero), 0: row-major (m, n/blk)
+    // The quantised result may be a column block of a wider operand (the N-sharded layer gathers its quantised output):
+    int q_ld;                  // bytes per row of the packed operand q_packed points into (n/2 when it is just this result)
+    int q_sf_cols;             // scale columns per row of that operand (n/blk when it is just this result)
+    int q_sf_col0;             // scale column of this result's column 0 inside it (a multiple of 4)
+    int q_n_peers;             // fused all-gather of the quantised result: the same bytes are also stored to the copies of
+    uint8_t* q_peer_packed[7]; // the operand in other GPUs' memory (peer-mapped; same layout, same offsets)
+    uint8_t* q_peer_sf[7];
     // fp32 partial result for a K-sharded GEMM (kEpiPartial): rows [j * rs_rows, (j + 1) * rs_rows) go, row stride n,
     // to rs_dst[j] -- the slab this rank owns inside rank j's staging buffer (peer-mapped for j != this rank)
     float* rs_dst[8];
@@ -507,8 +514,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 constexpr int BLK = SF_VEC;                 // elements per scale block
                 constexpr int NB = 64 / BLK;                // blocks per 64-column group (4 or 2)
                 const int row = row0 + lane;
-                const int sf_cols = p.n / BLK;
+                const int sf_cols = p.q_sf_cols;              // of the whole operand this result is a column block of
                 const int k_atoms = (sf_cols + 3) / 4;
+                const int sf_cols_here = p.n / BLK;           // scale columns this GEMM produces
+                // the zero padding up to a multiple of 4 scale columns belongs to the block that ends the operand;
+                // a block with a neighbour to its right must not write past its own columns
+                const int sf_cols_limit = (p.q_sf_col0 + sf_cols_here == sf_cols) ? k_atoms * 4 - p.q_sf_col0 : sf_cols_here;
                 const int rows_pad = ((p.m + 127) / 128) * 128;
 #pragma unroll
                 for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
@@ -523,23 +534,49 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         if (colg + b * BLK >= p.n || row >= p.m) code = 0;   // padding of the scale layout is zero
                         codes |= code << (8 * b);
                     }
+                    const size_t pk_off = static_cast<size_t>(row) * p.q_ld + colg / 2;
                     if (row < p.m) {
-                        uint8_t* dst = p.q_packed + static_cast<size_t>(row) * (p.n / 2) + colg / 2;
+                        if (colg + 64 <= p.n && (p.q_ld & 15) == 0) {
+                            // whole group, rows 16-byte aligned: 32 bytes per row as two 128-bit stores (the form that
+                            // also goes to the peers; the host admits peers only for such shapes)
+                            const uint4 lo = make_uint4(w[0], w[1], w[2], w[3]), hi = make_uint4(w[4], w[5], w[6], w[7]);
+                            uint4* dst = reinterpret_cast<uint4*>(p.q_packed + pk_off);
+                            dst[0] = lo;
+                            dst[1] = hi;
+                            for (int pi = 0; pi < p.q_n_peers; ++pi) {
+                                uint4* pd = reinterpret_cast<uint4*>(p.q_peer_packed[pi] + pk_off);
+                                __stcs(pd, lo);
+                                __stcs(pd + 1, hi);
+                            }
+                        } else {
+                            uint8_t* dst = p.q_packed + pk_off;
 #pragma unroll
-                        for (int h = 0; h < 4; ++h)     // 16 columns = 8 bytes each; N % 16 == 0
-                            if (colg + h * 16 < p.n) *reinterpret_cast<uint2*>(dst + h * 8) = make_uint2(w[2 * h], w[2 * h + 1]);
+                            for (int h = 0; h < 4; ++h)     // 16 columns = 8 bytes each; N % 16 == 0
+                                if (colg + h * 16 < p.n) *reinterpret_cast<uint2*>(dst + h * 8) = make_uint2(w[2 * h], w[2 * h + 1]);
+                        }
                     }
-                    const int c = colg / BLK;           // first scale column of the group (multiple of NB)
+                    const int c = colg / BLK;           // first scale column of the group (multiple of NB) in this result
+                    const int cg = p.q_sf_col0 + c;     // ... and in the operand it is a block of
                     if (p.q_tiled) {
-                        if (row < rows_pad && c < k_atoms * 4) {
-                            uint8_t* sp = p.q_sf + sf_tiled_offset(row, c, k_atoms);
-                            if constexpr (NB == 4) *reinterpret_cast<uint32_t*>(sp) = codes;
-                            else *reinterpret_cast<uint16_t*>(sp) = static_cast<uint16_t>(codes);
+                        if (row < rows_pad && c < sf_cols_limit) {
+                            const long long so = sf_tiled_offset(row, cg, k_atoms);
+                            if constexpr (NB == 4) {
+                                *reinterpret_cast<uint32_t*>(p.q_sf + so) = codes;
+                                for (int pi = 0; pi < p.q_n_peers; ++pi) __stcs(reinterpret_cast<uint32_t*>(p.q_peer_sf[pi] + so), codes);
+                            } else {
+                                *reinterpret_cast<uint16_t*>(p.q_sf + so) = static_cast<uint16_t>(codes);
+                                for (int pi = 0; pi < p.q_n_peers; ++pi)
+                                    __stcs(reinterpret_cast<unsigned short*>(p.q_peer_sf[pi] + so), static_cast<unsigned short>(codes));
+                            }
                         }
                     } else if (row < p.m) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
-                            if (c + b < sf_cols) p.q_sf[static_cast<size_t>(row) * sf_cols + c + b] = static_cast<uint8_t>(codes >> (8 * b));
+                            if (c + b < sf_cols_here) {
+                                const size_t so = static_cast<size_t>(row) * sf_cols + cg + b;
+                                p.q_sf[so] = static_cast<uint8_t>(codes >> (8 * b));
+                                for (int pi = 0; pi < p.q_n_peers; ++pi) p.q_peer_sf[pi][so] = static_cast<uint8_t>(codes >> (8 * b));
+                            }
                     }
                 }
             }

@@ -496,6 +496,61 @@ def gemm_quantized_out_transposed_b(A: Fp4Operand, B: Fp4Operand, out_global_sca
     return (q, res) if want else q
 
 
+def gemm_allgather_quantized_transposed_b(A: Fp4Operand, B: Fp4Operand, gathered: Fp4Operand, col0: int,
+                                          peer_packed_ptrs: list[int], peer_scale_ptrs: list[int],
+                                          bias: torch.Tensor | None = None, activation: str | None = None,
+                                          variant: int = GEMM_AUTO) -> Fp4Operand:
+    """``act(A @ B.T + bias)`` quantised in the GEMM epilogue as columns ``[col0, col0 + N)`` of ``gathered`` (an
+    (M, N_total) operand of A's format with tiled or row-major scales, NVFP4 with its static ``global_scale``) and,
+    fused into the same epilogue, stored to the other ranks' copies of that operand: ``peer_packed_ptrs`` /
+    ``peer_scale_ptrs`` are raw device addresses (valid on this GPU) of the bases of their packed bytes and scales.
+    The all-gather of an N-sharded layer's output in the form the next layer's GEMM consumes."""
+    fmt = A.fmt
+    name = _FMT_NAME[fmt]
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(k for k in ACTIVATIONS if k)}, got {activation!r}.")
+    if B.fmt != fmt or gathered.fmt != fmt:
+        raise ValueError(f"A, B and the gathered operand must all be {name} operands.")
+    m, k, n = A.rows, A.k, B.rows
+    if B.k != k:
+        raise ValueError(f"A and B must share K, got {k} and {B.k}.")
+    if m <= 64:
+        raise ValueError(f"the fused all-gather needs M > 64, got {m}.")
+    n_total = gathered.k
+    if gathered.rows != m:
+        raise ValueError(f"the gathered operand must have {m} rows, got {gathered.rows}.")
+    if n % 64 or col0 % 64 or n_total % 64 or col0 < 0 or col0 + n > n_total:
+        raise ValueError(f"N, col0 and N_total must be multiples of 64 with col0 + N <= N_total, got {n}, {col0}, {n_total}.")
+    if len(peer_packed_ptrs) != len(peer_scale_ptrs) or len(peer_packed_ptrs) > 7:
+        raise ValueError("one packed and one scale address per peer, at most 7 peers.")
+    if fmt == NVFP4 and (A.global_scale is None or B.global_scale is None or gathered.global_scale is None):
+        raise ValueError("NVFP4 operands need a global_scale tensor (the gathered operand a static one).")
+    if A.tile_major or B.tile_major or gathered.tile_major:
+        raise ValueError("tile-major operands serve the decode kernel only.")
+    if bias is not None and (bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,) or bias.device != A.device
+                             or not bias.is_contiguous() or bias.data_ptr() % 16 != 0):
+        raise ValueError(f"bias must be a contiguous, 16-byte aligned bfloat16 tensor of shape ({n},) on {A.device}.")
+    dev = _require_cuda(A.packed, "A")
+    if B.device != A.device or gathered.device != A.device:
+        raise ValueError(f"B and the gathered operand must be on device {A.device}.")
+    A = to_tiled(A)
+    B = to_tiled(B)
+    with torch.cuda.device(dev):
+        L = _lib.ensure_init(dev)
+        epi = _lib.Epilogue(None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], 1)
+        epi.q_packed = gathered.packed.data_ptr()
+        epi.q_scales = gathered.scales.data_ptr()
+        epi.q_global_scale = None if gathered.global_scale is None else gathered.global_scale.data_ptr()
+        epi.q_sf_layout = gathered.sf_layout
+        np_ = len(peer_packed_ptrs)
+        pk = (ctypes.c_void_p * max(np_, 1))(*peer_packed_ptrs)
+        ps = (ctypes.c_void_p * max(np_, 1))(*peer_scale_ptrs)
+        _lib.check(L.ave_fp4_gemm_allgather_quantized(_ptr(A.packed), _ptr(A.scales), _ptr(A.global_scale), _ptr(B.packed),
+                                                      _ptr(B.scales), _ptr(B.global_scale), m, n, k, fmt, variant, ctypes.byref(epi),
+                                                      n_total, col0, pk, ps, np_, _stream(A.device)))
+    return gathered
+
+
 def gemm_allgather_transposed_b(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor, peer_ptrs: list[int],
                                 variant: int = GEMM_AUTO) -> torch.Tensor:
     """``out = A @ B.T`` and, fused into the epilogue, the same tiles stored to ``peer_ptrs``: raw device

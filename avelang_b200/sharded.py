@@ -14,8 +14,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from .fp4_gemm import (Fp4Operand, gemm_allgather_transposed_b, gemm_mxfp4_transposed_b, gemm_nvfp4_transposed_b,
-                       gemm_partials_transposed_b, reduce_partials, NVFP4)
+from .fp4_gemm import (Fp4Operand, gemm_allgather_quantized_transposed_b, gemm_allgather_transposed_b, gemm_mxfp4_transposed_b,
+                       gemm_nvfp4_transposed_b, gemm_partials_transposed_b, reduce_partials, sf_bytes, NVFP4, SF_TILED)
 
 
 def shard_bounds(n: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
@@ -121,6 +121,62 @@ class ShardedFp4Linear:
         if self.world > 1:
             dist.all_gather_into_tensor(self._gathered.view(-1, n_local), local, group=self.group)
         return self._gathered
+
+
+class ShardedFp4LinearQuantizedOut:
+    """Column-parallel ``y = act(x @ W.T + bias)`` whose output is gathered as the NEXT layer's FP4 operand.
+
+    When the consumer of the gathered activations is another FP4 GEMM, the ranks need not exchange bf16: the GEMM
+    epilogue quantises its tile (blocks along N, the next layer's K) and stores the packed bytes and scale bytes
+    straight into every rank's copy of the (M, N) operand (symmetric memory, plain peer stores over NVLink) --
+    0.5625 byte per element (NVFP4) instead of 2.  ``forward`` returns that operand (scales in the tiled layout the GEMM
+    consumes); its bytes equal ``quantize_nvfp4(y, global_scale=out_global_scale)`` / ``quantize_mxfp4(y)`` of the
+    unsharded bf16 result.  NVFP4 needs a static tensor scale for the output, the same on every rank.
+    """
+
+    def __init__(self, weight_shard: Fp4Operand, out_global_scale: torch.Tensor | None = None, group=None):
+        self.weight = weight_shard
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if weight_shard.fmt == NVFP4 and out_global_scale is None:
+            raise ValueError("an NVFP4 output needs out_global_scale: a 1-element float32 tensor, the same on every rank.")
+        self.out_gs = out_global_scale if weight_shard.fmt == NVFP4 else None
+        self._op: Fp4Operand | None = None
+        self._hdl = None
+        self._peer_packed: list[int] = []
+        self._peer_sf: list[int] = []
+
+    def _buffers(self, m: int, n_local: int, device: torch.device) -> None:
+        n_total = n_local * self.world
+        if self._op is not None and self._op.shape == (m, n_total):
+            return
+        fmt = self.weight.fmt
+        pk_bytes = m * n_total // 2
+        sf_b = sf_bytes(m, n_total, fmt, SF_TILED)
+        pk_pad = (pk_bytes + 255) // 256 * 256
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            buf = symm.empty((pk_pad + sf_b,), dtype=torch.uint8, device=device)
+            self._hdl = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            order = [(self.rank + i) % self.world for i in range(1, self.world)]
+            self._peer_packed = [int(self._hdl.buffer_ptrs[p]) for p in order]
+            self._peer_sf = [int(self._hdl.buffer_ptrs[p]) + pk_pad for p in order]
+        else:
+            buf = torch.empty((pk_pad + sf_b,), dtype=torch.uint8, device=device)
+        self._op = Fp4Operand(buf[:pk_bytes].view(m, n_total // 2), buf[pk_pad:pk_pad + sf_b], self.out_gs, fmt, m, n_total, SF_TILED)
+
+    def forward(self, x: Fp4Operand, bias: torch.Tensor | None = None, activation: str | None = None) -> Fp4Operand:
+        """Returns the gathered (M, N) operand (its buffer is reused between calls: every rank must be done with the
+        previous result before any rank calls forward again)."""
+        m, n_local = x.rows, self.weight.rows
+        self._buffers(m, n_local, x.device)
+        gemm_allgather_quantized_transposed_b(x, self.weight, self._op, self.rank * n_local, self._peer_packed, self._peer_sf,
+                                              bias=bias, activation=activation)
+        if self._hdl is not None:
+            self._hdl.barrier()
+        return self._op
 
 
 def k_shard_bounds(k: int, world: int, rank: int, align: int = 256) -> tuple[int, int]:

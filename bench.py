@@ -56,8 +56,8 @@ MIN_TIMED_MS = 250.0             # the K steps are repeated until the timed regi
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, copied from the ncu captures summarised under profiles/
 # (a capture cannot be taken inside a benchmark run; `traffic_source` in the line names the summary)
 NCU_TRAFFIC = {
-    "gemm_8192": (250_128_768, "profiles/gemm_fp4_kernel_8192_nvfp4.md (ncu, mean of two launches)"),
-    "decode": (137_693_000, "profiles/gemm_fp4_skinny_kernel_decode_16x28672x8192.md (ncu)"),
+    "gemm_8192": (246_600_000, "profiles/choice_tile_shape_and_pipeline_depth.md, row 2-CTA 256x256 at 8192^3 (ncu, mean of two launches)"),
+    "decode": (134_600_000, "profiles/choice_decode_burst_and_stream_k.md, row burst 4 with stream-K (ncu, mean of two launches)"),
 }
 
 
@@ -394,12 +394,16 @@ def run_ours(args) -> dict:
     value = world * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
     gemm_tflops = flops_per_gpu / (gemm_ms * 1e-3) / 1e12
 
+    # The kernel is timed inside a region of several hundred milliseconds, so the denominator is the SUSTAINED
+    # figure of the measured peaks (the burst one applies to a kernel timed alone); both fractions are in the line.
+    fp4_peak_sustained = 4.0 * peaks["bf16_sustained"]
     roofline = {
         "bound": "tensor", "kernel": "gemm_fp4_kernel<2-CTA, 256x256x256>", "achieved": round(gemm_tflops, 1),
-        "peak": round(fp4_peak, 1), "unit": "TFLOP/s", "frac": round(gemm_tflops / fp4_peak, 4),
-        "peak_source": f"4 x cuBLAS bf16 burst ({peaks['bf16']:.0f} TF, {peaks['source']}): FP4 issues at 4x the bf16 rate",
+        "peak": round(fp4_peak_sustained, 1), "unit": "TFLOP/s", "frac": round(gemm_tflops / fp4_peak_sustained, 4),
+        "peak_source": (f"4 x cuBLAS bf16 sustained ({peaks['bf16_sustained']:.0f} TF, {peaks['source']}; the kernel is timed inside a "
+                        f">= {MIN_TIMED_MS:.0f} ms loop under the power cap): FP4 issues at 4x the bf16 rate"),
         "frac_of_nominal_9000": round(gemm_tflops / NOMINAL_FP4_TFLOPS, 4),
-        "frac_of_4x_sustained_bf16": round(gemm_tflops / (4.0 * peaks["bf16_sustained"]), 4),
+        "frac_of_4x_burst_bf16": round(gemm_tflops / fp4_peak, 4),
         "algorithmic_bytes": M * K // 2 + n_local * K // 2 + (M + n_local) * K // 16 + 2 * M * n_local,
         "traffic": NCU_TRAFFIC["gemm_8192"][0] if n_local == N else None,
         "traffic_source": NCU_TRAFFIC["gemm_8192"][1] if n_local == N else None,
@@ -441,6 +445,13 @@ def run_ours(args) -> dict:
             clocks["sm_mhz_in_kernel_error"] = repr(exc)
 
     e2e = e2e_block(B, head, n_local, R, args)
+    fp4_gather = None
+    if world > 1 and not args.skip_fp4_gather:
+        try:
+            fp4_gather = fp4_gather_block(B, head, n_local, R, args, fp4_peak)
+        except Exception as exc:
+            fp4_gather = {"error": repr(exc)[:300]}
+        B.barrier()
 
     cfg = make_config(world, args.workload)
     out = {
@@ -458,6 +469,8 @@ def run_ours(args) -> dict:
         out["exchange"] = "fused peer stores" if head["fused"] else "nccl"
     if head["parity"] is not None:
         out["parity"] = head["parity"]
+    if fp4_gather is not None:
+        out["fp4_gather"] = fp4_gather
 
     # free the headline's buffers before the side workloads
     del head, A_ops, B_ops, outs, layers, host_a
@@ -575,6 +588,47 @@ def e2e_block(B: Bench, head: dict, n_local: int, R: int, args) -> dict:
             "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * n_local * world,
             "h2d_bytes_per_step_per_rank": 2 * M * K // world, "d2h_bytes_per_step_per_rank": 2 * M * n_local,
             "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps, "what": what}
+
+
+def fp4_gather_block(B: Bench, head: dict, n_local: int, R: int, args, fp4_peak: float) -> dict:
+    """The same sharded layer gathering its output as the NEXT layer's NVFP4 operand: the GEMM epilogue quantises
+    its tile and stores packed bytes + scale bytes into every rank's copy (0.5625 byte per element over NVLink
+    instead of 2).  Checked against the quantise kernel applied to the gathered bf16 result, then timed."""
+    torch, ave = B.torch, B.ave
+    from avelang_b200 import sharded
+
+    world, rank, dev = B.world, B.rank, B.dev
+    A_ops, B_ops, layers = head["A"], head["B"], head["layers"]
+    n_total = n_local * world
+    g = layers[0].forward(A_ops[0])
+    B.barrier()
+    full = sharded.columns_view(g).reshape(M, n_total)          # the gathered bf16 result as one (M, N) matrix
+    gs = (full.float().abs().max() / 2688.0).reshape(1)         # static tensor scale of the output, same on every rank
+    want = ave.quantize_nvfp4(full, global_scale=gs)
+    qlayers = [sharded.ShardedFp4LinearQuantizedOut(B_ops[i], out_global_scale=gs) for i in range(2)]
+    op = qlayers[0].forward(A_ops[0])
+    B.barrier()
+    ok = bool(torch.equal(op.packed, want.packed)) and bool(torch.equal(op.scales, want.scales))
+    ok = B.all_true(ok)
+    del full, want
+    B.barrier()
+
+    def step(i: int):
+        qlayers[i % 2].forward(A_ops[i % R])
+
+    ms, reps = B.timed(step, args.steps, 3, 60.0)
+    ave.check_device_status(dev)
+    flops = 2.0 * M * n_local * K
+    link_bytes = M * n_local * (0.5 + 1.0 / 16.0) * (world - 1)
+    t_flop = flops / (fp4_peak * 1e12)
+    t_link = link_bytes / (NVLINK_GBS_PER_DIR * 1e9)
+    return {"what": "GEMM with quantising epilogue + peer stores of the packed bytes and scale bytes (the next layer's NVFP4 "
+                    "operand is gathered instead of the bf16 matrix) + device barrier",
+            "parity_gathered_operand_equals_quantise_of_gathered_bf16": ok,
+            "step_ms": round(ms, 4), "whole_job_tflops": round(world * flops / (ms * 1e-3) / 1e12, 1),
+            "nvlink_bytes_in_per_gpu": int(link_bytes), "nvlink_ingress_gbs": round(link_bytes / (ms * 1e-3) / 1e9, 1),
+            "target_ms": round(max(t_flop, t_link) * 1e3, 4), "frac": round(max(t_flop, t_link) * 1e3 / ms, 4),
+            "bound": "nvlink" if t_link > t_flop else "tensor", "bf16_gather_step_ms": round(head["step_ms"], 4)}
 
 
 def c3_block(B: Bench, fp4_peak: float, args) -> dict:
@@ -975,6 +1029,7 @@ def main():
     ap.add_argument("--skip-c3", action="store_true")
     ap.add_argument("--skip-c4", action="store_true")
     ap.add_argument("--skip-context", action="store_true")
+    ap.add_argument("--skip-fp4-gather", action="store_true")
     ap.add_argument("--workload", default="c1", choices=["c1", "c3"],
                     help="headline workload. c1: 8192^3 per GPU (weak scaling); c3: 8192 x 57344 x 8192 with N split over the GPUs")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: exchange with NCCL after the GEMM instead of the fused epilogue")

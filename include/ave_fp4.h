@@ -233,6 +233,26 @@ int ave_fp4_gemm_allgather(const void* a_packed, const void* a_scales, const voi
                            int64_t m, int64_t n, int64_t k, int64_t ldd, int fmt, int variant, void* stream);
 
 /*
+ * GEMM fused with the all-gather of its QUANTISED output: for an N-sharded layer whose consumer is another FP4
+ * GEMM, the ranks gather the next layer's operand (0.5 byte per element + one scale byte per block) instead of
+ * the bf16 matrix (2 bytes per element), about 3.5 times fewer bytes over NVLink.  As ave_fp4_gemm_epilogue with
+ * quantize_out (bias and activation allowed, tiled kernels, M > 64, d_bf16 not written): this rank's (m, n) result
+ * is quantised in the epilogue, blocks along N, as columns [col0, col0 + n) of a gathered (m, n_total) operand.
+ * epilogue->q_packed / q_scales point at the BASE of this rank's copy of that operand ((m, n_total / 2) bytes and
+ * ave_fp4_sf_bytes(m, n_total, fmt, q_sf_layout) scale bytes); peer_q_packed[i] / peer_q_scales[i] are device
+ * pointers, valid on THIS GPU, to the bases of the other ranks' copies (peer-mapped memory), to which the
+ * epilogue stores the same bytes at the same offsets with plain peer stores (no TMA, no multicast).  NVFP4 needs
+ * a static tensor scale of the result (epilogue->q_global_scale), the same on every rank.  n, col0 and n_total must
+ * be multiples of 64.  The caller synchronises the ranks afterwards (all kernels done) before any rank reads its
+ * copy; padding rows of a tiled scale layout are written by every rank for its own columns.  The bytes are those of
+ * ave_fp4_quantize applied to the bf16-rounded unsharded result.  No counterpart in the reference.
+ */
+int ave_fp4_gemm_allgather_quantized(const void* a_packed, const void* a_scales, const void* a_global_scale, const void* b_packed,
+                                     const void* b_scales, const void* b_global_scale, int64_t m, int64_t n, int64_t k, int fmt,
+                                     int variant, const ave_fp4_epilogue* epilogue, int64_t n_total, int64_t col0,
+                                     void* const* peer_q_packed, void* const* peer_q_scales, int n_peers, void* stream);
+
+/*
  * K-sharded GEMM + reduce-scatter in two calls (row-parallel linear layer on one NVLink/NVSwitch box).  No counterpart
  * in the reference, which has no multi-GPU code.
  *

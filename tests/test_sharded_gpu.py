@@ -1,6 +1,6 @@
 """GPU tier, needs >= 2 GPUs (skipped otherwise): N-sharded GEMM with the NCCL all-gather and with the
 all-gather fused into the GEMM epilogue (peer stores over NVLink) give the same bits, equal to the
-unsharded GEMM."""
+unsharded GEMM; and the form that gathers the quantised output gives the quantise kernel's bytes."""
 import os
 import socket
 import subprocess
@@ -38,6 +38,15 @@ for fused in (False, True):
         logical = sharded.columns_view(g).reshape(m, n)
         ok = ok and bool(torch.equal(logical, full))
         dist.barrier()
+# the same layer gathering its output as the next layer's FP4 operand (quantising epilogue + peer stores)
+gs_out = torch.tensor([float(full.float().abs().max()) / 2688.0], dtype=torch.float32, device=dev)
+want = ave.quantize_nvfp4(full, global_scale=gs_out)
+qlayer = sharded.ShardedFp4LinearQuantizedOut(shard, out_global_scale=gs_out)
+for _ in range(2):
+    op = qlayer.forward(A)
+    torch.cuda.synchronize(); dist.barrier()
+    ok = ok and bool(torch.equal(op.packed, want.packed)) and bool(torch.equal(op.scales, want.scales))
+    dist.barrier()
 ave.check_device_status(dev)
 print(f"rank {rank} ok={ok}", flush=True)
 dist.destroy_process_group()
