@@ -1122,8 +1122,10 @@ int ave_fp4_gemm_allgather_quantized(const void* a_packed, const void* a_scales,
     if (n_peers > 0 && (peer_q_packed == nullptr || peer_q_scales == nullptr))
         return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: peer pointer arrays are NULL");
     for (int i = 0; i < n_peers; ++i)
-        if (!peer_q_packed[i] || !peer_q_scales[i] || !aligned16(peer_q_packed[i]) || !aligned16(peer_q_scales[i]))
-            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: peer pointer %d is null or misaligned", i);
+        if (!peer_q_packed[i] || !peer_q_scales[i] || (reinterpret_cast<uintptr_t>(peer_q_packed[i]) & 31u) || !aligned16(peer_q_scales[i]))
+            return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: peer pointer %d is null or misaligned (packed: 32 bytes, scales: 16)", i);
+    if (reinterpret_cast<uintptr_t>(epilogue->q_packed) & 31u)
+        return fail(-AVE_FP4_ERR_ARG, "ave_fp4_gemm_allgather_quantized: q_packed must be 32-byte aligned");
     // every rank's block is whole 64-column groups (32 packed bytes, 4 NVFP4 / 2 MXFP4 scale columns of one tile row)
     if (n <= 0 || n % 64 != 0 || col0 < 0 || col0 % 64 != 0 || n_total % 64 != 0 || col0 + n > n_total)
         return fail(-AVE_FP4_ERR_ARG,

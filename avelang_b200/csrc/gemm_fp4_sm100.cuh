@@ -26,6 +26,13 @@
 
 namespace avefp4 {
 
+// 256-bit store (one whole 32-byte sector per lane), streaming.
+__device__ __forceinline__ void st_global_v8_cs(void* ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
 enum GemmStatus : int {
     kStatusOk = 0,
     kStatusTimeoutProducer = 101,
@@ -178,7 +185,10 @@ struct GemmConfig {
     static constexpr int kOffSfa = kOffB + STAGES * kBBytes;
     static constexpr int kOffSfb = kOffSfa + STAGES * kSfaBytes;
     static constexpr int kOffEpi = kOffSfb + STAGES * kSfbBytes;
-    static constexpr int kOffBar = kOffEpi + kEpiBytes;
+    // staging of the quantising epilogue's scale tiles: per column half two 512-byte tile images (double-buffered)
+    static constexpr int kSfStageBytes = kDense ? 0 : 2 * 2 * 512;
+    static constexpr int kOffSfStage = kOffEpi + kEpiBytes;
+    static constexpr int kOffBar = kOffSfStage + kSfStageBytes;
     static constexpr int kNumBars = 2 * STAGES + 2 * ACC_STAGES;
     static constexpr int kOffTmemPtr = kOffBar + kNumBars * 8;
     static constexpr int kSmemBytes = kOffTmemPtr + 16 + 1024;  // + slack for 1024-byte alignment
@@ -459,6 +469,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         const int my_groups = (half == 0) ? Cfg::kEpiGroups0 : Cfg::kEpiGroups1;   // warp-uniform
         const int my_col = (half == 0) ? 0 : Cfg::kEpiGroups0 * 64;
         int tile_iter = 0;
+        int sf_stage_parity = 0;     // which of the two scale-tile images of this column half is written next
         for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
             int tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
@@ -536,18 +547,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     }
                     const size_t pk_off = static_cast<size_t>(row) * p.q_ld + colg / 2;
                     if (row < p.m) {
-                        if (colg + 64 <= p.n && (p.q_ld & 15) == 0) {
-                            // whole group, rows 16-byte aligned: 32 bytes per row as two 128-bit stores (the form that
-                            // also goes to the peers; the host admits peers only for such shapes)
-                            const uint4 lo = make_uint4(w[0], w[1], w[2], w[3]), hi = make_uint4(w[4], w[5], w[6], w[7]);
-                            uint4* dst = reinterpret_cast<uint4*>(p.q_packed + pk_off);
-                            dst[0] = lo;
-                            dst[1] = hi;
-                            for (int pi = 0; pi < p.q_n_peers; ++pi) {
-                                uint4* pd = reinterpret_cast<uint4*>(p.q_peer_packed[pi] + pk_off);
-                                __stcs(pd, lo);
-                                __stcs(pd + 1, hi);
-                            }
+                        if (colg + 64 <= p.n && ((p.q_ld | static_cast<int>(reinterpret_cast<uintptr_t>(p.q_packed))) & 31) == 0) {
+                            // whole group, rows 32-byte aligned: the row's 32 bytes as one 256-bit store, i.e. one whole
+                            // sector per lane (the form that also goes to the peers; the host admits peers only for such
+                            // shapes -- over NVLink a store of part of a sector costs as much as a whole one)
+                            st_global_v8_cs(p.q_packed + pk_off, w);
+                            for (int pi = 0; pi < p.q_n_peers; ++pi) st_global_v8_cs(p.q_peer_packed[pi] + pk_off, w);
                         } else {
                             uint8_t* dst = p.q_packed + pk_off;
 #pragma unroll
@@ -561,8 +566,24 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         if (row < rows_pad && c < sf_cols_limit) {
                             const long long so = sf_tiled_offset(row, cg, k_atoms);
                             if constexpr (NB == 4) {
-                                *reinterpret_cast<uint32_t*>(p.q_sf + so) = codes;
-                                for (int pi = 0; pi < p.q_n_peers; ++pi) __stcs(reinterpret_cast<uint32_t*>(p.q_peer_sf[pi] + so), codes);
+                                // One 64-column group of the CTA's 128 rows is exactly one 512-byte scale tile, spread
+                                // over the four quadrant warps (16-byte slot l holds rows l, l+32, l+64, l+96).  The warps
+                                // put their 4 bytes per row into a tile image in shared memory and the first of them
+                                // writes the image as 512 contiguous bytes -- four whole lines -- to this GPU and the
+                                // peers, instead of 128 scattered 4-byte stores.  (All four warps take this branch
+                                // together: the conditions above depend on the tile and the group only.)
+                                const uint32_t img = smem_base + Cfg::kOffSfStage + (half * 2 + (sf_stage_parity & 1)) * 512;
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(img + lane * 16 + quad * 4), "r"(codes) : "memory");
+                                asm volatile("bar.sync %0, 128;" ::"r"(3 + half) : "memory");
+                                if (quad == 0) {
+                                    uint32_t v0, v1, v2, v3;
+                                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(img + lane * 16) : "memory");
+                                    const long long tile_off = sf_tiled_offset(row0 - quad * 32, cg, k_atoms) + lane * 16;
+                                    *reinterpret_cast<uint4*>(p.q_sf + tile_off) = make_uint4(v0, v1, v2, v3);
+                                    for (int pi = 0; pi < p.q_n_peers; ++pi)
+                                        __stcs(reinterpret_cast<uint4*>(p.q_peer_sf[pi] + tile_off), make_uint4(v0, v1, v2, v3));
+                                }
+                                ++sf_stage_parity;
                             } else {
                                 *reinterpret_cast<uint16_t*>(p.q_sf + so) = static_cast<uint16_t>(codes);
                                 for (int pi = 0; pi < p.q_n_peers; ++pi)
