@@ -8,6 +8,9 @@ served by the same TMA + tcgen05 pipeline as the FP4 kernels in dense bf16 mode
 instead of truncated (amdgpu_gemm.py:322-328 truncates), which is what the reference's own oracle
 ``(A.float() @ B.float().T).to(torch.bfloat16)`` does; and M, N need not be multiples of 128
 (edges are zero-filled on load and clipped on store) -- only K % 8 and N % 8 are required.
+
+The argument checks and their messages follow the reference operator (causalflow-ai/avelang,
+python/avelang_kernels/amdgpu_gemm.py, Apache-2.0) so that callers see the same errors.
 """
 from __future__ import annotations
 

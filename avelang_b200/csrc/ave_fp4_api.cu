@@ -569,7 +569,7 @@ int resolve_variant(int variant, int64_t m, int64_t n) {
 // another runtime's memory pool has no allocator of its own to ask, and a serving loop that
 // must never stall cannot afford the implicit device-wide synchronisation cudaMalloc/cudaFree
 // may cause.  For them the stream-K scratch of the skinny kernel lives in this fixed array,
-// which every GPU that loads the library holds (about 2.5 MiB) until the process exits.
+// which every GPU that loads the library holds (about 2.56 MiB) until the process exits.
 constexpr int kNoAllocMaxM = 16;          // one MMA-N step of activation rows
 constexpr int kNoAllocMaxN = 65536;       // 512 weight tiles
 constexpr int kNoAllocMaxCtas = 160;      // persistent CTAs (one per SM)

@@ -7,6 +7,9 @@ captured in a CUDA graph, events around repeat x iters replays, flops = 2*M*N*K,
 printed key=value line, optional validation with max-abs printed) -- for the block-scaled
 FP4 operators, and adds --format, --seed, --variant, --rotate and --no-graph.
 
+The bf16 mode's driver (flags, print format, validation block) follows the reference script
+(causalflow-ai/avelang, benchmark/gemm/bench_amdgpu_gemm.py, Apache-2.0).
+
 Validation uses the CPU oracle (dequantise E2M1 x scale, fp32 matmul, bf16 round) on the same
 quantised operands; it is meant for sizes the CPU finishes in seconds.
 """

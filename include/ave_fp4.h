@@ -279,7 +279,7 @@ int ave_fp4_reduce_partials(const void* slabs_f32, int world, int64_t rows, int6
  * It has no counterpart in the reference.  It exists for hosts that cannot call cudaMalloc:
  * a plugin living inside another runtime's memory pool, or a serving loop that must not risk
  * the device-wide stall an allocation can cause.  The stream-K scratch of the skinny kernel is
- * a fixed array inside the library instead (about 2.5 MiB, held by every GPU that loads the
+ * a fixed array inside the library instead (about 2.56 MiB, held by every GPU that loads the
  * library until the process exits).  Same arguments and result as ave_fp4_gemm with the skinny
  * variant; shapes beyond the limits are rejected with an error, not served some other way.
  * The first call on a device looks the array's device address up, so make that first call

@@ -135,3 +135,23 @@ def test_gemm_rejects_n_not_multiple_of_8_before_any_launch(lib):
     peers = (ctypes.c_void_p * 1)(4096)
     rc = lib.ave_fp4_gemm_allgather(dummy, dummy, None, dummy, dummy, None, dummy, peers, 1, 128, 132, 256, 136, 1, 0, None)
     assert rc == -1 and b"N must be a multiple of 8" in lib.ave_fp4_last_error()
+
+
+def test_operators_are_importable_under_the_reference_package_name():
+    """`python/avelang_kernels/` mirrors the reference's package layout (python/avelang_kernels/amdgpu_gemm.py)."""
+    import importlib
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "python"))
+    try:
+        nv = importlib.import_module("avelang_kernels.nvfp4_gemm")
+        amd = importlib.import_module("avelang_kernels.amdgpu_gemm")
+    finally:
+        sys.path.remove(os.path.join(ROOT, "python"))
+    assert nv.gemm_nvfp4_transposed_b is ave.gemm_nvfp4_transposed_b
+    assert nv.quantize_mxfp4 is ave.quantize_mxfp4 and nv.linear_nvfp4_decode is ave.linear_nvfp4_decode
+    from avelang_b200 import bf16_gemm
+
+    assert amd.gemm_pipeline_transposed_b is bf16_gemm.gemm_pipeline_transposed_b
+    with pytest.raises(ValueError, match="torch.bfloat16"):
+        amd.gemm_pipeline_transposed_b(torch.zeros((128, 64)), torch.zeros((128, 64), dtype=torch.bfloat16))
