@@ -485,6 +485,8 @@ def run_ours(args) -> dict:
 
     if not c3_headline and not args.skip_c3:
         side("c3", lambda: c3_block(B, fp4_peak, args))
+    if world > 1 and not args.skip_ksharded:
+        side("k_sharded", lambda: ksharded_block(B, fp4_peak, args))
     if world == 1:
         if not args.skip_decode:
             side("decode", lambda: decode_bench(ave, torch, dev, peaks))
@@ -629,6 +631,53 @@ def fp4_gather_block(B: Bench, head: dict, n_local: int, R: int, args, fp4_peak:
             "nvlink_bytes_in_per_gpu": int(link_bytes), "nvlink_ingress_gbs": round(link_bytes / (ms * 1e-3) / 1e9, 1),
             "target_ms": round(max(t_flop, t_link) * 1e3, 4), "frac": round(max(t_flop, t_link) * 1e3 / ms, 4),
             "bound": "nvlink" if t_link > t_flop else "tensor", "bf16_gather_step_ms": round(head["step_ms"], 4)}
+
+
+def ksharded_block(B: Bench, fp4_peak: float, args) -> dict:
+    """The other split of a linear layer: K-sharded (row-parallel) GEMM + reduce-scatter, M = N = 8192 and K = 8192 per
+    rank.  The fused form (fp32 partial tiles stored by the epilogue straight into the owner's staging buffer, then a slab
+    sum) is checked, bit for bit, against the same arithmetic done on this GPU alone with every rank's regenerated
+    operands, and against local partials + NCCL reduce-scatter; then both forms are timed."""
+    torch, ave = B.torch, B.ave
+    from avelang_b200 import fp4_gemm, sharded
+
+    world, rank, dev = B.world, B.rank, B.dev
+    rows = M // world
+
+    def operands(r):
+        return B.operand(M, K, 300_000 + r)[0], B.operand(N, K, 400_000 + r, std=0.02)[0]
+
+    A, W = operands(rank)
+    fused = sharded.RowShardedFp4Linear(W, fused=True)
+    got = fused.forward(A).clone()
+    B.barrier()
+    nccl = sharded.RowShardedFp4Linear(W, fused=False)
+    got_nccl = nccl.forward(A).clone()
+    B.barrier()
+    # this rank's rows computed alone: every rank's partial of them, summed in rank order by the same kernels
+    staging = torch.empty((world, rows, N), dtype=torch.float32, device=dev)
+    scratch = torch.empty((world, rows, N), dtype=torch.float32, device=dev)
+    for p in range(world):
+        Ap, Wp = (A, W) if p == rank else operands(p)
+        fp4_gemm.gemm_partials_transposed_b(Ap, Wp, [scratch[j].data_ptr() for j in range(world)], first_owner=(p + 1) % world)
+        staging[p].copy_(scratch[rank])
+    want = fp4_gemm.reduce_partials(staging)
+    torch.cuda.synchronize(dev)
+    ok = B.all_true(bool(torch.equal(got, want)))
+    ok_nccl = B.all_true(bool(torch.equal(got_nccl, got)))
+    del staging, scratch, want, got_nccl
+    B.barrier()
+    steps = 10
+    fused_ms, _ = B.timed(lambda i: fused.forward(A), steps, 3, 0.0)
+    nccl_ms, _ = B.timed(lambda i: nccl.forward(A), steps, 3, 0.0)
+    ave.check_device_status(dev)
+    link_bytes = 4.0 * M * N * (world - 1) / world
+    floor_ms = max(2.0 * M * N * K / (fp4_peak * 1e12), link_bytes / (NVLINK_GBS_PER_DIR * 1e9)) * 1e3
+    return {"workload": f"row_parallel_8192x8192x8192_per_rank_nvfp4_x{world}",
+            "parity_fused_equals_single_gpu_recomputation": ok, "parity_fused_equals_nccl_reduce_scatter": ok_nccl,
+            "fused_ms_per_step": round(fused_ms, 4), "nccl_ms_per_step": round(nccl_ms, 4),
+            "fused_tflops_whole_box": round(2.0 * M * N * K * world / (fused_ms * 1e-3) / 1e12, 1),
+            "nvlink_bytes_out_per_gpu": int(link_bytes), "floor_ms": round(floor_ms, 4), "frac_of_floor": round(floor_ms / fused_ms, 4)}
 
 
 def c3_block(B: Bench, fp4_peak: float, args) -> dict:
@@ -1030,6 +1079,7 @@ def main():
     ap.add_argument("--skip-c4", action="store_true")
     ap.add_argument("--skip-context", action="store_true")
     ap.add_argument("--skip-fp4-gather", action="store_true")
+    ap.add_argument("--skip-ksharded", action="store_true")
     ap.add_argument("--workload", default="c1", choices=["c1", "c3"],
                     help="headline workload. c1: 8192^3 per GPU (weak scaling); c3: 8192 x 57344 x 8192 with N split over the GPUs")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: exchange with NCCL after the GEMM instead of the fused epilogue")
