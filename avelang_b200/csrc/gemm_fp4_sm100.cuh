@@ -574,7 +574,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                                 // together: the conditions above depend on the tile and the group only.)
                                 const uint32_t img = smem_base + Cfg::kOffSfStage + (half * 2 + (sf_stage_parity & 1)) * 512;
                                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(img + lane * 16 + quad * 4), "r"(codes) : "memory");
-                                asm volatile("bar.sync %0, 128;" ::"r"(3 + half) : "memory");
+                                if (half == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                                else asm volatile("bar.sync 4, 128;" ::: "memory");
                                 if (quad == 0) {
                                     uint32_t v0, v1, v2, v3;
                                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(img + lane * 16) : "memory");

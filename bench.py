@@ -385,7 +385,7 @@ def run_ours(args) -> dict:
     fp4_peak = 4.0 * peaks["bf16"]
 
     sampler = ClockSampler(local) if rank == 0 else None
-    head = sharded_block(B, n_local, R, args.steps, warmup, MIN_TIMED_MS, "headline", keep_host_a=True)
+    head = sharded_block(B, n_local, R, args.steps, warmup, args.min_timed_ms, "headline", keep_host_a=True)
     clocks = sampler.stop() if sampler else None
     ave.check_device_status(dev)
     A_ops, B_ops, outs, layers, host_a = head["A"], head["B"], head["outs"], head["layers"], head["host_a"]
@@ -462,7 +462,7 @@ def run_ours(args) -> dict:
         "config": cfg, "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * head["reps"], "clocks": clocks,
         "pct_of_nominal_fp4_peak": round(100.0 * value / world / NOMINAL_FP4_TFLOPS, 2),
         "timed_repeats": head["reps"], "timed_region_ms": round(ms_per_step * args.steps * head["reps"], 1),
-        "timed_region": (f"{args.steps} steps x {head['reps']} repeats inside one CUDA-event pair (>= {MIN_TIMED_MS:.0f} ms), "
+        "timed_region": (f"{args.steps} steps x {head['reps']} repeats inside one CUDA-event pair (>= {args.min_timed_ms:.0f} ms), "
                          "barrier + synchronize on both sides, max over ranks"),
     }
     if world > 1:
@@ -1080,6 +1080,8 @@ def main():
     ap.add_argument("--skip-context", action="store_true")
     ap.add_argument("--skip-fp4-gather", action="store_true")
     ap.add_argument("--skip-ksharded", action="store_true")
+    ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,
+                    help="the K steps are repeated until the timed region is this long (0: time the K steps once, e.g. under a profiler)")
     ap.add_argument("--workload", default="c1", choices=["c1", "c3"],
                     help="headline workload. c1: 8192^3 per GPU (weak scaling); c3: 8192 x 57344 x 8192 with N split over the GPUs")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: exchange with NCCL after the GEMM instead of the fused epilogue")
