@@ -442,9 +442,8 @@ int64_t skinny_workspace_bytes(int64_t m, int64_t n, int sm_count) {
     return kSkinnyHdrBytes + skinny_counter_region(n) + static_cast<int64_t>(sm_count) * 2 * skinny_mp(m) * 128 * 4;
 }
 
-// Scratch of ave_fp4_linear_decode: the decode kernel's scratch, then the quantised activations (MP rows of packed
-// bytes and their tiled scales; written for inspection by the kernel that quantises in shared memory, and the real
-// operand of the two-launch fallback), then two floats (tensor scale, amax) for that fallback.
+// Scratch of ave_fp4_linear_decode: the decode kernel's scratch, then the quantised activations the quantise kernel
+// writes and the GEMM reads (packed bytes of up to MP rows and their tiled scales), then two floats (tensor scale, amax).
 struct FusedScratch {
     int64_t packed, sf, gs, total;
 };
