@@ -532,6 +532,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 // a block with a neighbour to its right must not write past its own columns
                 const int sf_cols_limit = (p.q_sf_col0 + sf_cols_here == sf_cols) ? k_atoms * 4 - p.q_sf_col0 : sf_cols_here;
                 const int rows_pad = ((p.m + 127) / 128) * 128;
+                // Whole 128-byte rows of packed output: with 256-column tiles, no bf16 output (the staging buffers are
+                // free) and the tile inside N, the two warps of a lane quadrant (column halves) put their 64 bytes per row
+                // side by side in one 4 KB staging buffer and then write 32 rows x 128 bytes as whole lines, eight lanes per
+                // row -- to this GPU and to the peers, where a 128-byte store uses NVLink four times better than 32-byte ones.
+                // The conditions depend on the tile and the launch only, so both warps agree.
+                const bool line_rows = (BLOCK_N == 256) && (p.d == nullptr) && (tn * BLOCK_N + BLOCK_N <= p.n) &&
+                                       (((p.q_ld | static_cast<int>(reinterpret_cast<uintptr_t>(p.q_packed))) & 15) == 0);
+                const uint32_t qbuf = smem_base + Cfg::kOffEpi + (((warp - 2) & 3) + 4 * (tile_iter & 1)) * Cfg::kEpiBufBytes;
 #pragma unroll
                 for (int g = 0; g < Cfg::kEpiGroups0; ++g) {
                     if (g >= my_groups) break;
@@ -546,7 +554,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         codes |= code << (8 * b);
                     }
                     const size_t pk_off = static_cast<size_t>(row) * p.q_ld + colg / 2;
-                    if (row < p.m) {
+                    if (line_rows) {
+                        // lane = row; 16-byte chunk q of the 128-byte row lives at chunk q ^ (row & 7)
+                        const int q0 = (half * Cfg::kEpiGroups0 + g) * 2;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(qbuf + lane * 128 + ((q0 ^ (lane & 7)) << 4)),
+                                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(qbuf + lane * 128 + (((q0 + 1) ^ (lane & 7)) << 4)),
+                                     "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                    } else if (row < p.m) {
                         if (colg + 64 <= p.n && ((p.q_ld | static_cast<int>(reinterpret_cast<uintptr_t>(p.q_packed))) & 31) == 0) {
                             // whole group, rows 32-byte aligned: the row's 32 bytes as one 256-bit store, i.e. one whole
                             // sector per lane (the form that also goes to the peers; the host admits peers only for such
@@ -599,6 +614,33 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                                 p.q_sf[so] = static_cast<uint8_t>(codes >> (8 * b));
                                 for (int pi = 0; pi < p.q_n_peers; ++pi) p.q_peer_sf[pi][so] = static_cast<uint8_t>(codes >> (8 * b));
                             }
+                    }
+                }
+                if (line_rows) {
+                    // both column halves of this quadrant have staged their 64 bytes per row (one named barrier per quadrant;
+                    // the buffer alternates with the tile, so the next tile's staging cannot overtake this read-out)
+                    switch (quad) {
+                        case 0: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+                        case 1: asm volatile("bar.sync 6, 64;" ::: "memory"); break;
+                        case 2: asm volatile("bar.sync 7, 64;" ::: "memory"); break;
+                        default: asm volatile("bar.sync 8, 64;" ::: "memory"); break;
+                    }
+                    // each of the two warps writes 16 of the 32 rows: eight lanes per 128-byte row, four rows per instruction
+                    const int q = lane & 7;
+                    const size_t col_off = static_cast<size_t>(tn) * (BLOCK_N / 2) + q * 16;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = half * 16 + i * 4 + (lane >> 3);
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                     : "r"(qbuf + r * 128 + ((q ^ (r & 7)) << 4)) : "memory");
+                        const int grow = row0 + r;
+                        if (grow < p.m) {
+                            const size_t off = static_cast<size_t>(grow) * p.q_ld + col_off;
+                            *reinterpret_cast<uint4*>(p.q_packed + off) = make_uint4(v0, v1, v2, v3);
+                            for (int pi = 0; pi < p.q_n_peers; ++pi)
+                                __stcs(reinterpret_cast<uint4*>(p.q_peer_packed[pi] + off), make_uint4(v0, v1, v2, v3));
+                        }
                     }
                 }
             }

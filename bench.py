@@ -177,6 +177,33 @@ class ClockSampler:
                 "reasons": reasons, "source": "nvml" if self.thread is not None else "nvidia-smi"}
 
 
+def bind_to_gpu_local_cpus(gpu_index: int):
+    """Run this rank's threads on the CPUs NVML names as local to its GPU, so that the pinned host buffers it allocates
+    afterwards sit on that NUMA node and the PCIe copies do not cross sockets (a process setting, not a GPU one).
+    Returns the number of CPUs bound to, or None when NVML or the call is unavailable."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = gpu_index
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                phys = int(ids[gpu_index])
+        h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return len(allowed)
+    except Exception:
+        return None
+
+
 def dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -202,6 +229,9 @@ class Bench:
             raise SystemExit("bench.py needs a CUDA device: the FP4 path has no CPU fallback")
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
+        self.cpu_affinity = None
+        if self.world > 1:
+            self.cpu_affinity = bind_to_gpu_local_cpus(self.local)
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.dev)
         self.peaks = measured_peaks()
@@ -467,6 +497,7 @@ def run_ours(args) -> dict:
     }
     if world > 1:
         out["exchange"] = "fused peer stores" if head["fused"] else "nccl"
+        out["cpus_bound_per_rank"] = B.cpu_affinity
     if head["parity"] is not None:
         out["parity"] = head["parity"]
     if fp4_gather is not None:
@@ -666,8 +697,13 @@ def ksharded_block(B: Bench, fp4_peak: float, args) -> dict:
     want = fp4_gemm.reduce_partials(staging)
     torch.cuda.synchronize(dev)
     ok = B.all_true(bool(torch.equal(got, want)))
-    ok_nccl = B.all_true(bool(torch.equal(got_nccl, got)))
-    del staging, scratch, want, got_nccl
+    # NCCL sums the fp32 partials in its own order (ring / tree), so beyond two ranks its bf16 result may differ from the
+    # rank-order sum in the last place: compared within the GEMM tolerance (relative Frobenius 1e-3), bit equality reported
+    diff = (got_nccl.float() - got.float())
+    rel = float(torch.linalg.norm(diff) / torch.linalg.norm(got.float()))
+    rel = B.max_over_ranks(rel)
+    bit_equal_nccl = B.all_true(bool(torch.equal(got_nccl, got)))
+    del staging, scratch, want, got_nccl, diff
     B.barrier()
     steps = 10
     fused_ms, _ = B.timed(lambda i: fused.forward(A), steps, 3, 0.0)
@@ -676,7 +712,9 @@ def ksharded_block(B: Bench, fp4_peak: float, args) -> dict:
     link_bytes = 4.0 * M * N * (world - 1) / world
     floor_ms = max(2.0 * M * N * K / (fp4_peak * 1e12), link_bytes / (NVLINK_GBS_PER_DIR * 1e9)) * 1e3
     return {"workload": f"row_parallel_8192x8192x8192_per_rank_nvfp4_x{world}",
-            "parity_fused_equals_single_gpu_recomputation": ok, "parity_fused_equals_nccl_reduce_scatter": ok_nccl,
+            "parity_fused_equals_single_gpu_recomputation": ok,
+            "nccl_reduce_scatter_form_rel_fro_vs_fused": round(rel, 8), "nccl_form_within_1e-3": rel <= 1e-3,
+            "nccl_form_bit_equal": bit_equal_nccl,
             "fused_ms_per_step": round(fused_ms, 4), "nccl_ms_per_step": round(nccl_ms, 4),
             "fused_tflops_whole_box": round(2.0 * M * N * K * world / (fused_ms * 1e-3) / 1e12, 1),
             "nvlink_bytes_out_per_gpu": int(link_bytes), "floor_ms": round(floor_ms, 4), "frac_of_floor": round(floor_ms / fused_ms, 4)}
