@@ -89,7 +89,9 @@ int64_t ave_fp4_sf_bytes(int64_t rows, int64_t k, int fmt, int sf_layout);
 /*
  * Bytes of zero-initialised scratch ave_fp4_gemm needs for this shape on `device`
  * (0 for shapes served by the tiled kernels).  The scratch must be all zero before
- * its first use; the kernel leaves it reusable for the next call on the same stream.
+ * its first use; the kernel leaves it reusable for the next call on the same stream,
+ * also for a call of a different shape (what has to be zero between calls sits in a
+ * prefix whose size does not depend on the shape, for N up to 524288).
  */
 int64_t ave_fp4_workspace_bytes(int64_t m, int64_t n, int64_t k, int fmt, int variant, int device);
 
@@ -113,7 +115,9 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
 
 /*
  * NVFP4 quantise with the tensor scale taken from the data (amax / 2688), in one call: for inputs of up
- * to 2^20 elements (decode activations) one 8-CTA cluster launch does amax and quantise together; above
+ * to 2^20 elements (decode activations) one 8-CTA cluster launch does amax and quantise together (up to 8192
+ * blocks of 16 elements, e.g. 16 x 8192, with one block per thread kept in registers across the exchange of the
+ * maxima -- the shortest dependent chain, which is what the decode GEMM queued behind it waits for); above
  * that it is ave_fp4_amax + ave_fp4_quantize and needs `amax_scratch` (4 bytes of device memory).
  * Results are identical to the two-call form.
  */

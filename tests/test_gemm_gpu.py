@@ -105,6 +105,14 @@ def test_skinny_many_tiles_short_k(cuda_device, oracle, fmt, m, n, k):
     assert torch.equal(outs[0], outs[1])
 
 
+def test_skinny_scratch_is_shared_across_shapes(cuda_device, oracle):
+    """One scratch buffer serves calls of different shapes one after the other: a small-N call that leaves stream-K
+    partials behind must not disturb the arrival counters of a following large-N call (everything that has to be zero
+    between calls sits in a shape-independent prefix of the scratch)."""
+    for m, n, k in ((9, 1160, 2080), (16, 28672, 1024), (32, 520, 2048), (16, 20480, 2048), (1, 128, 256), (16, 28672, 1024)):
+        _run_case(oracle, cuda_device, ave.NVFP4, m, n, k, ave.GEMM_SKINNY, a_kind="outlier", seed=m + n)
+
+
 def test_skinny_is_deterministic_and_reusable(cuda_device, oracle):
     """Stream-K partials are added in a fixed order, and the scratch counters return to zero,
     so back-to-back calls give identical bits."""
