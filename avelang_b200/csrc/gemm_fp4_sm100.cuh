@@ -601,9 +601,33 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                                 }
                                 ++sf_stage_parity;
                             } else {
-                                *reinterpret_cast<uint16_t*>(p.q_sf + so) = static_cast<uint16_t>(codes);
-                                for (int pi = 0; pi < p.q_n_peers; ++pi)
-                                    __stcs(reinterpret_cast<unsigned short*>(p.q_peer_sf[pi] + so), static_cast<unsigned short>(codes));
+                                // MXFP4: a group carries two scale columns, so with 256-column tiles the two groups of a
+                                // column half make one scale tile; staged like the NVFP4 one and written after the second
+                                // group, when both groups lie inside this result's columns and the result starts on a tile
+                                // boundary of the operand it is a block of (conditions of the tile and the launch alone)
+                                const bool staged = (BLOCK_N == 256) && (col0 / BLK + 4 <= sf_cols_limit) && ((p.q_sf_col0 & 3) == 0);
+                                if (staged) {
+                                    const uint32_t img = smem_base + Cfg::kOffSfStage + (half * 2 + (sf_stage_parity & 1)) * 512;
+                                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(img + lane * 16 + quad * 4 + (g & 1) * 2),
+                                                 "h"(static_cast<uint16_t>(codes)) : "memory");
+                                    if (g == 1) {
+                                        if (half == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                                        else asm volatile("bar.sync 4, 128;" ::: "memory");
+                                        if (quad == 0) {
+                                            uint32_t v0, v1, v2, v3;
+                                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(img + lane * 16) : "memory");
+                                            const long long tile_off = sf_tiled_offset(row0 - quad * 32, cg - 2, k_atoms) + lane * 16;
+                                            *reinterpret_cast<uint4*>(p.q_sf + tile_off) = make_uint4(v0, v1, v2, v3);
+                                            for (int pi = 0; pi < p.q_n_peers; ++pi)
+                                                __stcs(reinterpret_cast<uint4*>(p.q_peer_sf[pi] + tile_off), make_uint4(v0, v1, v2, v3));
+                                        }
+                                        ++sf_stage_parity;
+                                    }
+                                } else {
+                                    *reinterpret_cast<uint16_t*>(p.q_sf + so) = static_cast<uint16_t>(codes);
+                                    for (int pi = 0; pi < p.q_n_peers; ++pi)
+                                        __stcs(reinterpret_cast<unsigned short*>(p.q_peer_sf[pi] + so), static_cast<unsigned short>(codes));
+                                }
                             }
                         }
                     } else if (row < p.m) {
