@@ -98,7 +98,7 @@ class ShardedFp4Linear:
             slab_bytes = m * n_local * 2
             # this rank's slab inside every other rank's buffer; start with the next rank so that
             # the ranks do not all push to the same destination at once
-            order = [(self.rank + i) % self.world for i in range(1, self.world)]
+            order = peer_order(self.rank, self.world)
             self._peer_ptrs = [int(self._hdl.buffer_ptrs[p]) + self.rank * slab_bytes for p in order]
         else:
             self._gathered = torch.empty(shape, dtype=torch.bfloat16, device=device)
@@ -121,6 +121,27 @@ class ShardedFp4Linear:
         if self.world > 1:
             dist.all_gather_into_tensor(self._gathered.view(-1, n_local), local, group=self.group)
         return self._gathered
+
+
+def peer_order(rank: int, world: int) -> list[int]:
+    """The other ranks in the order this rank stores to them: starting with the next rank, so that at any moment the
+    ranks push to different destinations."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}.")
+    return [(rank + i) % world for i in range(1, world)]
+
+
+def quantized_gather_layout(m: int, n_local: int, world: int, rank: int, fmt: int) -> dict:
+    """Byte layout of one rank's copy of the gathered (M, world * n_local) FP4 operand inside its symmetric buffer:
+    packed bytes first, then (256-byte aligned) the tiled scales; plus this rank's first column in the operand."""
+    if n_local % 64 != 0:
+        raise ValueError(f"every rank's column block must be a multiple of 64 columns, got {n_local}.")
+    n_total = n_local * world
+    pk_bytes = m * n_total // 2
+    pk_pad = (pk_bytes + 255) // 256 * 256
+    sf_b = sf_bytes(m, n_total, fmt, SF_TILED)
+    return {"n_total": n_total, "packed_bytes": pk_bytes, "scales_offset": pk_pad, "scales_bytes": sf_b,
+            "total_bytes": pk_pad + sf_b, "col0": rank * n_local}
 
 
 class ShardedFp4LinearQuantizedOut:
@@ -148,23 +169,21 @@ class ShardedFp4LinearQuantizedOut:
         self._peer_sf: list[int] = []
 
     def _buffers(self, m: int, n_local: int, device: torch.device) -> None:
-        n_total = n_local * self.world
+        fmt = self.weight.fmt
+        lay = quantized_gather_layout(m, n_local, self.world, self.rank, fmt)
+        n_total, pk_bytes, pk_pad, sf_b = lay["n_total"], lay["packed_bytes"], lay["scales_offset"], lay["scales_bytes"]
         if self._op is not None and self._op.shape == (m, n_total):
             return
-        fmt = self.weight.fmt
-        pk_bytes = m * n_total // 2
-        sf_b = sf_bytes(m, n_total, fmt, SF_TILED)
-        pk_pad = (pk_bytes + 255) // 256 * 256
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm
 
-            buf = symm.empty((pk_pad + sf_b,), dtype=torch.uint8, device=device)
+            buf = symm.empty((lay["total_bytes"],), dtype=torch.uint8, device=device)
             self._hdl = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
-            order = [(self.rank + i) % self.world for i in range(1, self.world)]
+            order = peer_order(self.rank, self.world)
             self._peer_packed = [int(self._hdl.buffer_ptrs[p]) for p in order]
             self._peer_sf = [int(self._hdl.buffer_ptrs[p]) + pk_pad for p in order]
         else:
-            buf = torch.empty((pk_pad + sf_b,), dtype=torch.uint8, device=device)
+            buf = torch.empty((lay["total_bytes"],), dtype=torch.uint8, device=device)
         self._op = Fp4Operand(buf[:pk_bytes].view(m, n_total // 2), buf[pk_pad:pk_pad + sf_b], self.out_gs, fmt, m, n_total, SF_TILED)
 
     def forward(self, x: Fp4Operand, bias: torch.Tensor | None = None, activation: str | None = None) -> Fp4Operand:

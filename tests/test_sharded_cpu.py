@@ -136,3 +136,31 @@ def test_k_sharded_reduce_scatter_math_two_ranks():
         p.join(180)
         assert p.exitcode == 0
     assert ret[0] and ret[1]
+
+
+def test_quantized_gather_layout_and_peer_order():
+    """Host-side bookkeeping of the quantised all-gather: where each rank's column block sits in the gathered operand,
+    how the symmetric buffer is laid out, and in which order a rank stores to its peers (no GPU needed)."""
+    from avelang_b200 import fp4_gemm
+
+    for world in (1, 2, 4, 8):
+        seen_first = set()
+        for rank in range(world):
+            order = sharded.peer_order(rank, world)
+            assert sorted(order + [rank]) == list(range(world))          # every other rank exactly once
+            if world > 1:
+                assert order[0] == (rank + 1) % world
+                seen_first.add(order[0])
+        if world > 1:
+            assert len(seen_first) == world                                # the ranks start with different destinations
+    lay = sharded.quantized_gather_layout(8192, 7168, 8, 3, fp4_gemm.NVFP4)
+    assert lay["n_total"] == 57344 and lay["col0"] == 3 * 7168
+    assert lay["packed_bytes"] == 8192 * 57344 // 2 and lay["scales_offset"] % 256 == 0
+    assert lay["scales_bytes"] == fp4_gemm.sf_bytes(8192, 57344, fp4_gemm.NVFP4, fp4_gemm.SF_TILED) == 64 * 896 * 512
+    assert lay["total_bytes"] == lay["scales_offset"] + lay["scales_bytes"]
+    mx = sharded.quantized_gather_layout(300, 320, 4, 1, fp4_gemm.MXFP4)
+    assert mx["col0"] == 320 and mx["scales_bytes"] == 3 * 10 * 512 and mx["scales_offset"] == (300 * 640 + 255) // 256 * 256
+    with pytest.raises(ValueError, match="multiple of 64"):
+        sharded.quantized_gather_layout(128, 96, 2, 0, fp4_gemm.NVFP4)
+    with pytest.raises(ValueError, match="bad rank"):
+        sharded.peer_order(2, 2)
