@@ -55,5 +55,38 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+SHIM_SRC = os.path.join(_HERE, "..", "python", "src", "avefp4_shim.cc")
+SHIM_DIR = os.path.join(_HERE, "..", "python", "avelang_kernels")
+
+
+def shim_path() -> str:
+    import sysconfig
+
+    return os.path.join(SHIM_DIR, "_avefp4_shim" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_shim(force: bool = False) -> str:
+    """Compile python/src/avefp4_shim.cc (the pybind11 module over the C ABI) next to python/avelang_kernels,
+    linked against libavefp4.so through an rpath relative to the module.  The reference builds its native module
+    from the same directory with CMake (python/CMakeLists.txt:19); one g++ call is enough for a shim."""
+    import sysconfig
+
+    import pybind11
+
+    out = shim_path()
+    build()
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(os.path.getmtime(SHIM_SRC),
+                                                                        os.path.getmtime(os.path.join(_HERE, "..", "include", "ave_fp4.h"))):
+        return out
+    cxx = shutil.which("g++") or "/usr/bin/g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-I", pybind11.get_include(), "-I",
+           sysconfig.get_paths()["include"], SHIM_SRC, "-L", _HERE, "-lavefp4", "-Wl,-rpath,$ORIGIN/../../avelang_b200", "-o", out]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("building the pybind11 shim failed:\n" + proc.stdout)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force=True, verbose=True))
+    print(build_shim(force=True))

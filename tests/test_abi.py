@@ -155,3 +155,25 @@ def test_operators_are_importable_under_the_reference_package_name():
     assert amd.gemm_pipeline_transposed_b is bf16_gemm.gemm_pipeline_transposed_b
     with pytest.raises(ValueError, match="torch.bfloat16"):
         amd.gemm_pipeline_transposed_b(torch.zeros((128, 64)), torch.zeros((128, 64), dtype=torch.bfloat16))
+
+
+def test_native_module_builds_loads_and_forwards_to_the_c_abi(lib):
+    """python/src/avefp4_shim.cc: the pybind11 form of the binding (the reference keeps its native module in
+    python/src as well).  No GPU here: host arithmetic must agree with the C ABI and a launch must fail loudly."""
+    import importlib
+    import sys
+
+    build.build_shim()
+    sys.path.insert(0, os.path.join(ROOT, "python"))
+    try:
+        S = importlib.import_module("avelang_kernels._avefp4_shim")
+    finally:
+        sys.path.remove(os.path.join(ROOT, "python"))
+    for name in ("init", "gemm", "quantize", "quantize_nvfp4_dynamic", "linear_decode", "bf16_gemm", "check", "sf_bytes",
+                 "workspace_bytes", "linear_decode_workspace_bytes", "last_error", "sm_count"):
+        assert hasattr(S, name), name
+    for rows, k, fmt, layout in ((128, 512, 0, 1), (130, 96, 1, 1), (16, 8192, 0, 0)):
+        assert S.sf_bytes(rows, k, fmt, layout) == lib.ave_fp4_sf_bytes(rows, k, fmt, layout)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="ave-lang Error"):
+            S.gemm(4096, 4096, 0, 4096, 4096, 0, 4096, 128, 128, 128, 128, 0)

@@ -351,3 +351,31 @@ def test_agrees_with_library_nvfp4_gemm(cuda_device):
     ref = lib.float() * (A.global_scale * B.global_scale)
     rel = (torch.linalg.norm(ours - ref) / torch.linalg.norm(ref)).item()
     assert rel < 5e-3, rel
+
+
+def test_native_module_gives_the_same_bits_as_ctypes(cuda_device):
+    """The pybind11 module in python/src forwards to the same C ABI: tiled GEMM, decode GEMM (shared scratch) and a fused
+    epilogue through it equal the ctypes operators bit for bit."""
+    import importlib
+    import sys
+
+    from avelang_b200 import build
+
+    build.build_shim()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "python"))
+    try:
+        native = importlib.import_module("avelang_kernels.native")
+    finally:
+        sys.path.remove(os.path.join(root, "python"))
+    dev = cuda_device
+    for fmt, quant, gemm in ((ave.NVFP4, ave.quantize_nvfp4, ave.gemm_nvfp4_transposed_b), (ave.MXFP4, ave.quantize_mxfp4, ave.gemm_mxfp4_transposed_b)):
+        for m, n, k in ((256, 512, 1024), (16, 1160, 2080)):
+            A = quant(inputs.normal_bf16(m, k, 0).to(dev))
+            B = quant(inputs.normal_bf16(n, k, 1, std=0.02).to(dev))
+            bias = inputs.normal_bf16(1, n, 2).reshape(n).to(dev)
+            assert torch.equal(native.gemm_fp4_transposed_b(A, B), gemm(A, B))
+            assert torch.equal(native.gemm_fp4_transposed_b(A, B, bias=bias, activation="gelu_tanh"), gemm(A, B, bias=bias, activation="gelu_tanh"))
+    ave.check_device_status(dev)
+    with pytest.raises(ValueError, match="share K"):
+        native.gemm_fp4_transposed_b(A, ave.quantize_mxfp4(inputs.normal_bf16(64, 512, 3).to(dev)))
