@@ -554,7 +554,7 @@ def e2e_block(B: Bench, head: dict, n_local: int, R: int, args) -> dict:
     from avelang_b200 import sharded
 
     world, rank, dev = B.world, B.rank, B.dev
-    A_ops, B_ops, outs, host_a = head["A"], head["B"], head["outs"], head["host_a"]
+    B_ops, outs, host_a = head["B"], head["outs"], head["host_a"]
     # enough steps for the three-stage pipeline's fill and drain (one copy-in and one copy-out, ~5 ms, both inside the
     # timed region) not to dominate: 10 steps read 9 % low
     e2e_steps = max(40, 2 * args.steps)
@@ -632,7 +632,7 @@ def fp4_gather_block(B: Bench, head: dict, n_local: int, R: int, args, fp4_peak:
     torch, ave = B.torch, B.ave
     from avelang_b200 import sharded
 
-    world, rank, dev = B.world, B.rank, B.dev
+    world, dev = B.world, B.dev
     A_ops, B_ops, layers = head["A"], head["B"], head["layers"]
     n_total = n_local * world
     g = layers[0].forward(A_ops[0])
@@ -651,7 +651,7 @@ def fp4_gather_block(B: Bench, head: dict, n_local: int, R: int, args, fp4_peak:
     def step(i: int):
         qlayers[i % 2].forward(A_ops[i % R])
 
-    ms, reps = B.timed(step, args.steps, 3, 60.0)
+    ms, _ = B.timed(step, args.steps, 3, 60.0)
     ave.check_device_status(dev)
     flops = 2.0 * M * n_local * K
     link_bytes = M * n_local * (0.5 + 1.0 / 16.0) * (world - 1)
@@ -1058,7 +1058,7 @@ def run_reference(args) -> dict:
     """The reference arm: the oracle's CPU path on the host cores (the reference project has no FP4
     implementation and cannot be built here, so the oracle port is the reference for this path).
     One step = config 1 in full (all 8192 rows); rows are halved only if a full pass would not fit the time budget."""
-    world, rank, _ = dist_env()
+    _, rank, _ = dist_env()
     if rank != 0:
         return {}
     cores = claim_host_threads()
