@@ -62,10 +62,10 @@ def gemm_pipeline_transposed_b(
         raise ValueError(f"out must have dtype torch.bfloat16, got {out.dtype}.")
     elif out.device != A.device:
         raise ValueError(f"out must be on device {A.device}, got {out.device}.")
-    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
-        raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
     if m == 0 or n == 0:
         return out
+    if out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
 
     dev = A.device.index if A.device.index is not None else torch.cuda.current_device()
     with torch.cuda.device(dev):

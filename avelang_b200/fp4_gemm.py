@@ -290,7 +290,7 @@ def _gemm(A: Fp4Operand, B: Fp4Operand, out: torch.Tensor | None, fmt: int, vari
         raise ValueError(f"out must have dtype torch.bfloat16, got {out.dtype}.")
     elif out.device != A.device:
         raise ValueError(f"out must be on device {A.device}, got {out.device}.")
-    if out is not None and (out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0):
+    if out is not None and m > 0 and n > 0 and (out.stride(1) != 1 or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0):
         raise ValueError("out must be row-major with a row stride that is a multiple of 8 elements and 16-byte aligned.")
     if bias is not None:
         if bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,):

@@ -50,6 +50,9 @@ def test_out_and_validation(cuda_device):
         gemm_pipeline_transposed_b(A, B, out=torch.empty((256, 128), dtype=torch.bfloat16))
     with pytest.raises(ValueError, match="K must be"):
         gemm_pipeline_transposed_b(A[:, :4].contiguous(), B[:, :4].contiguous())
+    # no rows on either side: an empty result, nothing launched
+    assert tuple(gemm_pipeline_transposed_b(A[:0], B).shape) == (0, 128)
+    assert tuple(gemm_pipeline_transposed_b(A, B[:0]).shape) == (256, 0)
 
 
 def test_large_8192_against_row_sample(cuda_device):

@@ -175,6 +175,21 @@ def test_out_argument_and_row_stride(cuda_device, oracle):
         ave.gemm_nvfp4_transposed_b(A, B, out=torch.empty((m, n), dtype=torch.float16, device=cuda_device))
 
 
+@pytest.mark.parametrize("fmt", [ave.NVFP4, ave.MXFP4])
+def test_empty_operands(cuda_device, fmt):
+    """No activation rows or no weight rows: an empty result of the right shape, nothing launched, `out` returned."""
+    q = ave.quantize_nvfp4 if fmt == ave.NVFP4 else ave.quantize_mxfp4
+    g = ave.gemm_nvfp4_transposed_b if fmt == ave.NVFP4 else ave.gemm_mxfp4_transposed_b
+    k = 256
+    full = q(torch.randn((64, k), device=cuda_device).to(torch.bfloat16))
+    none = q(torch.zeros((0, k), dtype=torch.bfloat16, device=cuda_device))
+    assert tuple(g(none, full).shape) == (0, 64)
+    assert tuple(g(full, none).shape) == (64, 0)
+    out = torch.empty((0, 64), dtype=torch.bfloat16, device=cuda_device)
+    assert g(none, full, out=out) is out
+    ave.check_device_status(cuda_device)
+
+
 def test_global_scale_is_linear(cuda_device):
     """Scaling a tensor scale by a power of two scales the output exactly (size-independent property)."""
     m = n = k = 1024
