@@ -238,6 +238,14 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // The tiled kernels are launched with programmatic stream serialisation (their launch and set-up run under the tail of
 // the previous kernel in the stream; they wait for it on the device before touching memory): +2 % on back-to-back
 // 8192^3 launches.  The profiling stamps want launches that do not overlap; AVE_FP4_GEMM_PDL=0 switches it off for A/B timing.
+// Tile rows per band of the persistent schedule (decode_tile).  FP4: 16 (at 8192^3 the CTA-pair tiles run 2 % faster than
+// with 8, config 3's 57344 columns 6.7 %, 16384^3 1.9 %; 32 and more lose 10-25 % at 16384^3); dense bf16, whose operand
+// rows are four times as long, and the K-sharded schedule keep 8.  AVE_FP4_GEMM_BAND overrides (tuning aid).
+int gemm_band(int by_default) {
+    static const int v = [] { const char* e = getenv("AVE_FP4_GEMM_BAND"); return e ? atoi(e) : 0; }();
+    return v > 0 ? v : by_default;
+}
+
 int tiled_pdl(const DeviceState& ds) {
     static const bool pdl_off = [] { const char* e = getenv("AVE_FP4_GEMM_PDL"); return e != nullptr && e[0] == '0'; }();
     return (ds.trace == nullptr && !pdl_off) ? 1 : 0;
@@ -305,6 +313,7 @@ int launch_gemm(const DeviceState& ds, const void* a, const void* sfa, const flo
         }
     }
     p.pdl = tiled_pdl(ds);
+    p.band = gemm_band(rs_world > 0 ? 8 : 16);
     p.rs_world = rs_world;
     p.rs_rows = rs_world > 0 ? static_cast<int>(m / rs_world) : 0;
     for (int i = 0; i < 8; ++i) p.rs_dst[i] = (i < rs_world) ? static_cast<float*>(slabs[i]) : nullptr;
@@ -385,6 +394,7 @@ int launch_dense(const DeviceState& ds, const void* a, const void* b, void* d, i
     p.trace = ds.trace;
     p.trace_cap = ds.trace_cap;
     p.pdl = tiled_pdl(ds);
+    p.band = gemm_band(8);
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     long long clusters = ds.sm_count / CG;
     if (tiles < clusters) clusters = tiles;

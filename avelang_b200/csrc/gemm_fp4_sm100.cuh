@@ -92,6 +92,7 @@ struct GemmParams {
     int rs_world;
     int tm_perm_w;             // tile-row order of the schedule, see decode_tile: owners visited in turn (0 = off)
     int tm_first;              // first owner (tm_perm_w > 0) or cyclic shift of the tile rows (tm_perm_w = 0)
+    int band;                  // tile rows per band of the schedule (decode_tile), >= 1
     int pdl;                   // 1: launched with programmatic stream serialisation -- the grid may be scheduled while the
                                //    previous kernel in the stream still runs; it touches global memory only after that
                                //    kernel has finished (griddepcontrol.wait), so only launch and set-up are overlapped
@@ -205,15 +206,14 @@ struct GemmConfig {
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-// Tile index -> (tile_m, tile_n): bands of 8 tile rows, M fastest inside a band, so
-// concurrently running CTAs share a few A panels and a few B panels in L2.
+// Tile index -> (tile_m, tile_n): bands of `kGroup` tile rows (chosen by the host: 16 for FP4 operands, 8 for dense
+// bf16), M fastest inside a band, so concurrently running CTAs share a few A panels and a few B panels in L2.
 // K-sharded GEMMs scatter their tile rows to different owner GPUs, so the order of the tile rows decides where the
 // stores go at any moment.  With `perm_w` owners of tiles_m / perm_w tile rows each, consecutive positions of the schedule
 // visit the owners in turn, starting with owner `first` (position p -> owner (first + p mod w) mod w, its row p / w): every
 // rank sends to every owner all the time, NVLink traffic is spread over the whole kernel and no GPU's ingress is the target
 // of all ranks at once.  perm_w = 0: tile rows are only shifted cyclically by `first` (0 = the plain order).
-__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int perm_w, int first, int& tm, int& tn) {
-    constexpr int kGroup = 8;
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int perm_w, int first, int& tm, int& tn, int kGroup) {
     const int band = kGroup * tiles_n;
     const int g = t / band;
     const int first_row = g * kGroup;
@@ -312,7 +312,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int rec = 0;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 int tm, tn;
-                decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
+                decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn, p.band);
                 const int row_a = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * Cfg::kBlockM;
                 const int row_b = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBnCta;
                 const int sfa_atom0 = (row_a / 128) * p.sf_k_atoms;
@@ -389,7 +389,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 uint32_t sfb_shift = 0;
                 if constexpr (BLOCK_N % 128 != 0) {
                     int tm, tn;
-                    decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
+                    decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn, p.band);
                     sfb_shift = static_cast<uint32_t>(((tn * BLOCK_N) % 128) / 32);
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -472,7 +472,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         int sf_stage_parity = 0;     // which of the two scale-tile images of this column half is written next
         for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_iter) {
             int tm, tn;
-            decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn);
+            decode_tile(t, p.tiles_m, p.tiles_n, p.tm_perm_w, p.tm_first, tm, tn, p.band);
             const int acc = tile_iter % ACC_STAGES;
             const uint32_t acc_phase = static_cast<uint32_t>(tile_iter / ACC_STAGES) & 1u;
             const bool tr = (p.trace != nullptr) && (blockIdx.x == 0) && (warp == 2) && (lane == 0) && (tile_iter < p.trace_cap);
