@@ -690,16 +690,16 @@ int ave_fp4_init(int device) {
     g_dev[device].sm_count = prop.multiProcessorCount;
     {
         DeviceState& d = g_dev[device];
-        auto occ = [](auto kernel) {
+        auto occ = [](auto kernel, int threads = 256) {
             int n = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) n = 1;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
             return n;
         };
         d.occ_amax = occ(amax_bf16_kernel);
-        d.occ_quant[0][0] = occ(quantize_fp4_kernel<kFmtNvfp4, false>);
-        d.occ_quant[0][1] = occ(quantize_fp4_kernel<kFmtNvfp4, true>);
-        d.occ_quant[1][0] = occ(quantize_fp4_kernel<kFmtMxfp4, false>);
-        d.occ_quant[1][1] = occ(quantize_fp4_kernel<kFmtMxfp4, true>);
+        d.occ_quant[0][0] = occ(quantize_fp4_kernel<kFmtNvfp4, false>, kQuantThreads);
+        d.occ_quant[0][1] = occ(quantize_fp4_kernel<kFmtNvfp4, true>, kQuantThreads);
+        d.occ_quant[1][0] = occ(quantize_fp4_kernel<kFmtMxfp4, false>, kQuantThreads);
+        d.occ_quant[1][1] = occ(quantize_fp4_kernel<kFmtMxfp4, true>, kQuantThreads);
         d.occ_reduce = occ(reduce_partials_kernel);
     }
     g_dev[device].ready = true;
@@ -769,7 +769,8 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
     const bool tiled = (sf_layout == AVE_FP4_SF_TILED);
     const long long rows_pad = tiled ? ((rows + 127) / 128) * 128 : rows;
     const long long items = rows_pad * ((k + 1023) / 1024);  // one warp step each
-    long long blocks = (items + 7) / 8;
+    constexpr int kWarps = kQuantThreads / 32;
+    long long blocks = (items + kWarps - 1) / kWarps;
     const long long cap = static_cast<long long>(ds->sm_count) * ds->occ_quant[fmt == AVE_FP4_FMT_NVFP4 ? 0 : 1][tiled ? 1 : 0];
     if (blocks > cap) blocks = cap;   // one full wave of resident blocks; each walks the items with a grid stride
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(x_bf16);
@@ -782,7 +783,7 @@ int ave_fp4_quantize(const void* x_bf16, int64_t rows, int64_t k, int64_t ldx, i
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
+    cfg.blockDim = dim3(kQuantThreads, 1, 1);
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
