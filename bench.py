@@ -56,7 +56,7 @@ MIN_TIMED_MS = 250.0             # the K steps are repeated until the timed regi
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, copied from the ncu captures summarised under profiles/
 # (a capture cannot be taken inside a benchmark run; `traffic_source` in the line names the summary)
 NCU_TRAFFIC = {
-    "gemm_8192": (246_600_000, "profiles/choice_tile_shape_and_pipeline_depth.md, row 2-CTA 256x256 at 8192^3 (ncu, mean of two launches)"),
+    "gemm_8192": (205_100_000, "profiles/choice_tile_shape_and_pipeline_depth.md, row 2-CTA 256x256 at 8192^3 (ncu, mean of two launches)"),
     "decode": (134_600_000, "profiles/choice_decode_burst_and_stream_k.md, row burst 4 with stream-K (ncu, mean of two launches)"),
 }
 
